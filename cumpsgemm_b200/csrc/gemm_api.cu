@@ -1,0 +1,408 @@
+// Host dispatch of the TCEC GEMM and the C ABI around it.
+//
+// Reference counterparts: cumpsgemm::gemm<T> (src/cumpsgemm.cu:228-419),
+// cumpsgemm::gemm_stridedBatch<T> (:421-547), the extern "C" wrappers
+// (:549-605) and the AUTO / FP16TCEC_SCALING orchestration of the
+// interception layer (src/cumpsgemm_cublas.cu:445-577, :829-961).
+//
+// One call = split op(A) -> split op(B) -> tcgen05 GEMM, all on the handle's
+// stream.  The reference's module table (364 instantiations per arch,
+// src/instance_sm80.cu) collapses to three tile widths because op N/T/C,
+// leading dimensions and edges are absorbed by the split pass.
+#include "internal.hpp"
+
+#include <algorithm>
+#include <type_traits>
+
+namespace cumpsgemm_b200 {
+namespace {
+
+constexpr std::size_t kDefaultWorkspaceLimit = 8ull << 30;
+
+inline std::uint64_t round_up(std::uint64_t x, std::uint64_t a) { return (x + a - 1) / a * a; }
+
+bool ensure_workspace(cuMpSGEMM_handle *h, std::size_t bytes) {
+  if (h->workspace_bytes >= bytes) return true;
+  // cudaFree waits for work that may still read the old buffer.
+  if (h->workspace != nullptr) cudaFree(h->workspace);
+  h->workspace = nullptr;
+  h->workspace_bytes = 0;
+  if (cudaMalloc(&h->workspace, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  h->workspace_bytes = bytes;
+  return true;
+}
+
+__global__ void dyn_params_from_flag_kernel(DynParams *out, const int *flag) {
+  out->scale_a = 1.f;
+  out->scale_b = 1.f;
+  out->unscale_c = 1.f;
+  const int mode = flag_gemm_mode(*flag);
+  out->gemm_mode = (mode == CUMPSGEMM_TF32TCEC) ? CUMPSGEMM_TF32TCEC : CUMPSGEMM_FP16TCEC;
+}
+
+template <class T> struct Scalar;
+template <> struct Scalar<float> {
+  static float re(const float *p) { return *p; }
+  static float im(const float *) { return 0.f; }
+};
+template <> struct Scalar<cuComplex> {
+  static float re(const cuComplex *p) { return p->x; }
+  static float im(const cuComplex *p) { return p->y; }
+};
+
+int pick_tile_n(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
+                std::uint64_t batch) {
+  const char *force = std::getenv("CUMPSGEMM_TILE_N");
+  if (force != nullptr) {
+    const int v = std::atoi(force);
+    if (v == 256 || v == 128 || v == 64) return v;
+  }
+  const std::uint64_t tiles_m = (m_exp + 127) / 128;
+  for (int bn : {256, 128}) {
+    const std::uint64_t tiles = tiles_m * ((n + bn - 1) / bn) * batch;
+    if (tiles >= h->num_sms) return bn;
+  }
+  return 64;
+}
+
+} // namespace
+
+template <class T>
+cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperation_t op_B,
+                             std::uint64_t m, std::uint64_t n, std::uint64_t k, const T *alpha,
+                             const T *a, std::uint64_t lda, std::uint64_t stridea, const T *b,
+                             std::uint64_t ldb, std::uint64_t strideb, const T *beta, T *c,
+                             std::uint64_t ldc, std::uint64_t stridec, std::uint64_t batch,
+                             cuMpSGEMM_compute_mode_t mode, const DynParams *dyn,
+                             unsigned *used_kernel_module_id) {
+  constexpr bool is_complex = std::is_same<T, cuComplex>::value;
+  if (h == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  if (mode == CUMPSGEMM_DRY_RUN) return CUBLAS_STATUS_SUCCESS;
+  if (m == 0 || n == 0 || k == 0 || batch == 0 || alpha == nullptr || beta == nullptr ||
+      a == nullptr || b == nullptr || c == nullptr)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  const bool a_n = (op_A == CUBLAS_OP_N), b_n = (op_B == CUBLAS_OP_N);
+  if (lda < (a_n ? m : k) || ldb < (b_n ? k : n) || ldc < m) return CUBLAS_STATUS_INVALID_VALUE;
+  if (m > 0x3fffffffull || n > 0x7fffffffull || k > 0x3fffffffull || batch > 65535ull)
+    return CUBLAS_STATUS_INVALID_VALUE;
+
+  bool want_fp16 = false, want_tf32 = false, ec = true;
+  switch (mode) {
+  case CUMPSGEMM_FP16TCEC:
+    want_fp16 = true;
+    break;
+  case CUMPSGEMM_TF32TCEC:
+    want_tf32 = true;
+    break;
+  case CUMPSGEMM_FP16TC:
+    want_fp16 = true;
+    ec = false;
+    break;
+  case CUMPSGEMM_TF32TC:
+    want_tf32 = true;
+    ec = false;
+    break;
+  case CUMPSGEMM_AUTO:
+    want_fp16 = want_tf32 = true; // both launched, gated on the device-side decision
+    break;
+  default:
+    log_error(std::string("compute mode ") + cuMpSGEMM_get_compute_mode_string(mode) +
+              " is not computed by cuMpSGEMM kernels");
+    return CUBLAS_STATUS_NOT_SUPPORTED;
+  }
+
+  DeviceGuard guard(h->device);
+  if (mode == CUMPSGEMM_AUTO && dyn == nullptr) {
+    // Direct API use: the caller enabled a flag slot (or none: slot 0 = TF32TCEC).
+    DynParams *slot = h->dev_dyn_params + h->dyn_params_next;
+    h->dyn_params_next = (h->dyn_params_next + 1) % h->dyn_params_length;
+    const unsigned id = h->dyn_launch.enabled ? h->dyn_launch.enabled_id : 0u;
+    dyn_params_from_flag_kernel<<<1, 1, 0, h->cuda_stream>>>(slot, h->dyn_launch.flag_buffer + id);
+    dyn = slot;
+  }
+
+  const std::uint64_t fpe = is_complex ? 2 : 1;
+  const std::uint64_t m_exp = m * fpe; // rows of the expanded real problem
+  const std::uint64_t k_exp = k * fpe;
+  const int tile_n = pick_tile_n(h, m_exp, n, batch);
+  if (used_kernel_module_id != nullptr)
+    *used_kernel_module_id = (tile_n == 256) ? 0u : (tile_n == 128 ? 1u : 2u);
+
+  const std::uint32_t rows_pad_a = static_cast<std::uint32_t>(round_up(m_exp, 128));
+  const std::uint32_t rows_pad_b = static_cast<std::uint32_t>(round_up(n, tile_n));
+  const std::uint32_t k_pad = static_cast<std::uint32_t>(round_up(k_exp, 64));
+  const std::size_t es_max = want_tf32 ? 4 : 2;
+  const std::size_t planes = ec ? 2 : 1;
+  const std::size_t bytes_a_1 = planes * rows_pad_a * static_cast<std::size_t>(k_pad) * es_max;
+  const std::size_t bytes_b_1 = planes * rows_pad_b * static_cast<std::size_t>(k_pad) * es_max;
+  const std::size_t limit =
+      h->workspace_limit_bytes ? h->workspace_limit_bytes : kDefaultWorkspaceLimit;
+  std::uint64_t chunk = std::max<std::uint64_t>(1, limit / (bytes_a_1 + bytes_b_1));
+  chunk = std::min<std::uint64_t>(chunk, batch);
+  if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1))) {
+    log_error("failed to allocate the operand workspace");
+    return CUBLAS_STATUS_ALLOC_FAILED;
+  }
+  char *ws_a = reinterpret_cast<char *>(h->workspace);
+  char *ws_b = ws_a + chunk * bytes_a_1;
+
+  const bool prof = h->exp_stats.profiling_enabled;
+  if (prof) h->exp_stats.profiler.start("gemm_kernel", h->cuda_stream);
+  cudaError_t err = cudaSuccess;
+  for (std::uint64_t b0 = 0; b0 < batch && err == cudaSuccess; b0 += chunk) {
+    const std::uint32_t nb = static_cast<std::uint32_t>(std::min<std::uint64_t>(chunk, batch - b0));
+    for (int kind_i = 0; kind_i < 2 && err == cudaSuccess; ++kind_i) {
+      const SplitKind kind = kind_i == 0 ? SplitKind::fp16 : SplitKind::tf32;
+      if ((kind == SplitKind::fp16 && !want_fp16) || (kind == SplitKind::tf32 && !want_tf32))
+        continue;
+      SplitArgs sa;
+      sa.kind = kind;
+      sa.operand = Operand::A;
+      sa.is_complex = is_complex;
+      sa.conjugate = is_complex && op_A == CUBLAS_OP_C;
+      sa.src_k_contig = !a_n;
+      sa.rows = m;
+      sa.k = k;
+      sa.src = a + b0 * stridea;
+      sa.ld = lda;
+      sa.stride = stridea;
+      sa.batch = nb;
+      sa.panel = ws_a;
+      sa.rows_pad = rows_pad_a;
+      sa.k_pad = k_pad;
+      sa.with_lo = ec;
+      sa.dyn = dyn;
+      err = launch_split(sa, h->cuda_stream);
+      if (err != cudaSuccess) break;
+      SplitArgs sb = sa;
+      sb.operand = Operand::B;
+      sb.conjugate = is_complex && op_B == CUBLAS_OP_C;
+      sb.src_k_contig = b_n;
+      sb.rows = n;
+      sb.src = b + b0 * strideb;
+      sb.ld = ldb;
+      sb.stride = strideb;
+      sb.panel = ws_b;
+      sb.rows_pad = rows_pad_b;
+      err = launch_split(sb, h->cuda_stream);
+      if (err != cudaSuccess) break;
+
+      TcecGemmArgs g;
+      g.kind = kind;
+      g.error_correction = ec;
+      g.m = static_cast<std::uint32_t>(m_exp);
+      g.n = static_cast<std::uint32_t>(n);
+      g.k_pad = k_pad;
+      g.rows_pad_a = rows_pad_a;
+      g.rows_pad_b = rows_pad_b;
+      g.batch = nb;
+      g.panel_a = ws_a;
+      g.panel_b = ws_b;
+      g.c = reinterpret_cast<float *>(c + b0 * stridec);
+      g.ldc = ldc * fpe;
+      g.stride_c = stridec * fpe;
+      g.alpha_r = Scalar<T>::re(alpha);
+      g.alpha_i = Scalar<T>::im(alpha);
+      g.beta_r = Scalar<T>::re(beta);
+      g.beta_i = Scalar<T>::im(beta);
+      g.is_complex = is_complex;
+      g.dyn = dyn;
+      g.tile_n = tile_n;
+      g.dev_status = h->dev_status;
+      err = launch_tcec_gemm(g, h->cuda_stream);
+    }
+  }
+  if (prof) h->exp_stats.profiler.stop("gemm_kernel", h->cuda_stream);
+  if (err != cudaSuccess) {
+    log_error(std::string("kernel launch failed: ") + cudaGetErrorString(err));
+    return CUBLAS_STATUS_EXECUTION_FAILED;
+  }
+  return CUBLAS_STATUS_SUCCESS;
+}
+
+template <class T>
+cublasStatus_t gemm_with_statistics(cuMpSGEMM_handle *h, cublasOperation_t op_A,
+                                    cublasOperation_t op_B, std::uint64_t m, std::uint64_t n,
+                                    std::uint64_t k, const T *alpha, const T *a, std::uint64_t lda,
+                                    std::uint64_t stridea, const T *b, std::uint64_t ldb,
+                                    std::uint64_t strideb, const T *beta, T *c, std::uint64_t ldc,
+                                    std::uint64_t stridec, std::uint64_t batch,
+                                    cuMpSGEMM_compute_mode_t mode, unsigned *stats_id_a_out,
+                                    unsigned *stats_id_b_out, unsigned *flag_id_out) {
+  if (h == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  if (mode != CUMPSGEMM_AUTO && mode != CUMPSGEMM_FP16TCEC_SCALING)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  if (m == 0 || n == 0 || k == 0 || batch == 0 || a == nullptr || b == nullptr)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  if (m > 0xffffffffull || n > 0xffffffffull || k > 0xffffffffull || lda > 0xffffffffull ||
+      ldb > 0xffffffffull || stridea > 0xffffffffull || strideb > 0xffffffffull ||
+      batch > 0xffffffffull)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  DeviceGuard guard(h->device);
+  // stored extents of A and B (before op)
+  const unsigned am = static_cast<unsigned>(op_A == CUBLAS_OP_N ? m : k);
+  const unsigned an = static_cast<unsigned>(op_A == CUBLAS_OP_N ? k : m);
+  const unsigned bm = static_cast<unsigned>(op_B == CUBLAS_OP_N ? k : n);
+  const unsigned bn = static_cast<unsigned>(op_B == CUBLAS_OP_N ? n : k);
+  // A batch of one is a single matrix whatever the stride says.
+  const unsigned sa = batch > 1 ? static_cast<unsigned>(stridea) : 0u;
+  const unsigned sb = batch > 1 ? static_cast<unsigned>(strideb) : 0u;
+  unsigned id_a, id_b, flag_id;
+  cuMpSGEMM_compute_mode_t gemm_mode;
+  if (mode == CUMPSGEMM_AUTO) {
+    id_a = cumpsgemm::exp_stats_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
+                                       static_cast<unsigned>(batch), sa);
+    id_b = cumpsgemm::exp_stats_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
+                                       static_cast<unsigned>(batch), sb);
+    flag_id = next_dyn_launch_id(h);
+    cumpsgemm::set_dynamic_launch_buffer_by_exp_stats(h, flag_id, id_a, id_b);
+    gemm_mode = CUMPSGEMM_AUTO;
+  } else {
+    id_a = cumpsgemm::exp_max_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
+                                     static_cast<unsigned>(batch), sa);
+    id_b = cumpsgemm::exp_max_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
+                                     static_cast<unsigned>(batch), sb);
+    flag_id = 1; // reserved slot: FP16TCEC with both scale bits
+    gemm_mode = CUMPSGEMM_FP16TCEC;
+  }
+  if (stats_id_a_out) *stats_id_a_out = id_a;
+  if (stats_id_b_out) *stats_id_b_out = id_b;
+  if (flag_id_out) *flag_id_out = flag_id;
+  const DynParams *dyn = prepare_dyn_params(h, flag_id, id_a, id_b);
+  return gemm_dispatch<T>(h, op_A, op_B, m, n, k, alpha, a, lda, stridea, b, ldb, strideb, beta, c,
+                          ldc, stridec, batch, gemm_mode, dyn, nullptr);
+}
+
+#define INSTANTIATE(T)                                                                            \
+  template cublasStatus_t gemm_dispatch<T>(                                                       \
+      cuMpSGEMM_handle *, cublasOperation_t, cublasOperation_t, std::uint64_t, std::uint64_t,     \
+      std::uint64_t, const T *, const T *, std::uint64_t, std::uint64_t, const T *, std::uint64_t, \
+      std::uint64_t, const T *, T *, std::uint64_t, std::uint64_t, std::uint64_t,                 \
+      cuMpSGEMM_compute_mode_t, const DynParams *, unsigned *);                                   \
+  template cublasStatus_t gemm_with_statistics<T>(                                                \
+      cuMpSGEMM_handle *, cublasOperation_t, cublasOperation_t, std::uint64_t, std::uint64_t,     \
+      std::uint64_t, const T *, const T *, std::uint64_t, std::uint64_t, const T *, std::uint64_t, \
+      std::uint64_t, const T *, T *, std::uint64_t, std::uint64_t, std::uint64_t,                 \
+      cuMpSGEMM_compute_mode_t, unsigned *, unsigned *, unsigned *);
+INSTANTIATE(float)
+INSTANTIATE(cuComplex)
+#undef INSTANTIATE
+
+} // namespace cumpsgemm_b200
+
+// ---------------------------------------------------------------- public C++ API
+namespace cumpsgemm {
+using namespace cumpsgemm_b200;
+
+template <class T>
+cublasStatus_t gemm(cuMpSGEMM_handle_t handle, const cublasOperation_t op_A,
+                    const cublasOperation_t op_B, const uint64_t m, const uint64_t n,
+                    const uint64_t k, const T *alpha, const T *const a_dmem_ptr,
+                    const uint64_t lda, const T *const b_dmem_ptr, const uint64_t ldb,
+                    const T *beta, T *const c_dmem_ptr, const uint64_t ldc,
+                    const cuMpSGEMM_compute_mode_t compute_mode,
+                    unsigned *const used_kernel_module_id) {
+  if (compute_mode == CUMPSGEMM_FP16TCEC_SCALING) {
+    return gemm_with_statistics<T>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda, 0,
+                                   b_dmem_ptr, ldb, 0, beta, c_dmem_ptr, ldc, 0, 1, compute_mode,
+                                   nullptr, nullptr, nullptr);
+  }
+  return gemm_dispatch<T>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda, 0, b_dmem_ptr, ldb,
+                          0, beta, c_dmem_ptr, ldc, 0, 1, compute_mode, nullptr,
+                          used_kernel_module_id);
+}
+
+template <class T>
+cublasStatus_t gemm_stridedBatch(cuMpSGEMM_handle_t handle, const cublasOperation_t op_A,
+                                 const cublasOperation_t op_B, const uint64_t m, const uint64_t n,
+                                 const uint64_t k, const T *alpha, const T *const a_dmem_ptr,
+                                 const uint64_t lda, const uint64_t stridea,
+                                 const T *const b_dmem_ptr, const uint64_t ldb,
+                                 const uint64_t strideb, const T *beta, T *const c_dmem_ptr,
+                                 const uint64_t ldc, const uint64_t stridec,
+                                 const uint64_t batch_count,
+                                 const cuMpSGEMM_compute_mode_t compute_mode,
+                                 unsigned *const used_kernel_module_id) {
+  if (compute_mode == CUMPSGEMM_FP16TCEC_SCALING) {
+    return gemm_with_statistics<T>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda, stridea,
+                                   b_dmem_ptr, ldb, strideb, beta, c_dmem_ptr, ldc, stridec,
+                                   batch_count, compute_mode, nullptr, nullptr, nullptr);
+  }
+  return gemm_dispatch<T>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda, stridea,
+                          b_dmem_ptr, ldb, strideb, beta, c_dmem_ptr, ldc, stridec, batch_count,
+                          compute_mode, nullptr, used_kernel_module_id);
+}
+
+#define INSTANTIATE(T)                                                                           \
+  template cublasStatus_t gemm<T>(cuMpSGEMM_handle_t, const cublasOperation_t,                   \
+                                  const cublasOperation_t, const uint64_t, const uint64_t,       \
+                                  const uint64_t, const T *, const T *const, const uint64_t,     \
+                                  const T *const, const uint64_t, const T *, T *const,           \
+                                  const uint64_t, const cuMpSGEMM_compute_mode_t,                \
+                                  unsigned *const);                                              \
+  template cublasStatus_t gemm_stridedBatch<T>(                                                  \
+      cuMpSGEMM_handle_t, const cublasOperation_t, const cublasOperation_t, const uint64_t,      \
+      const uint64_t, const uint64_t, const T *, const T *const, const uint64_t, const uint64_t, \
+      const T *const, const uint64_t, const uint64_t, const T *, T *const, const uint64_t,       \
+      const uint64_t, const uint64_t, const cuMpSGEMM_compute_mode_t, unsigned *const);
+INSTANTIATE(float)
+INSTANTIATE(cuComplex)
+#undef INSTANTIATE
+} // namespace cumpsgemm
+
+// ---------------------------------------------------------------- C ABI
+extern "C" {
+
+cublasStatus_t cuMpSGEMM_sgemm(cuMpSGEMM_handle_t handle, const cublasOperation_t op_A,
+                               const cublasOperation_t op_B, const uint64_t m, const uint64_t n,
+                               const uint64_t k, const float *alpha, const float *const a_dmem_ptr,
+                               const uint64_t lda, const float *const b_dmem_ptr,
+                               const uint64_t ldb, const float *beta, float *const c_dmem_ptr,
+                               const uint64_t ldc, const cuMpSGEMM_compute_mode_t compute_mode) {
+  if (op_A == CUBLAS_OP_C || op_B == CUBLAS_OP_C) return CUBLAS_STATUS_INVALID_VALUE;
+  return cumpsgemm::gemm<float>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda, b_dmem_ptr,
+                                ldb, beta, c_dmem_ptr, ldc, compute_mode);
+}
+
+cublasStatus_t cuMpSGEMM_cgemm(cuMpSGEMM_handle_t handle, const cublasOperation_t op_A,
+                               const cublasOperation_t op_B, const uint64_t m, const uint64_t n,
+                               const uint64_t k, const cuComplex *alpha,
+                               const cuComplex *const a_dmem_ptr, const uint64_t lda,
+                               const cuComplex *const b_dmem_ptr, const uint64_t ldb,
+                               const cuComplex *beta, cuComplex *const c_dmem_ptr,
+                               const uint64_t ldc, const cuMpSGEMM_compute_mode_t compute_mode) {
+  return cumpsgemm::gemm<cuComplex>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda,
+                                    b_dmem_ptr, ldb, beta, c_dmem_ptr, ldc, compute_mode);
+}
+
+cublasStatus_t cuMpSGEMM_sgemm_strided_batch(
+    cuMpSGEMM_handle_t handle, const cublasOperation_t op_A, const cublasOperation_t op_B,
+    const uint64_t m, const uint64_t n, const uint64_t k, const float *alpha,
+    const float *const a_dmem_ptr, const uint64_t lda, const uint64_t stridea,
+    const float *const b_dmem_ptr, const uint64_t ldb, const uint64_t strideb, const float *beta,
+    float *const c_dmem_ptr, const uint64_t ldc, const uint64_t stridec,
+    const uint64_t batch_count, const cuMpSGEMM_compute_mode_t compute_mode) {
+  if (op_A == CUBLAS_OP_C || op_B == CUBLAS_OP_C) return CUBLAS_STATUS_INVALID_VALUE;
+  return cumpsgemm::gemm_stridedBatch<float>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr, lda,
+                                             stridea, b_dmem_ptr, ldb, strideb, beta, c_dmem_ptr,
+                                             ldc, stridec, batch_count, compute_mode);
+}
+
+cublasStatus_t cuMpSGEMM_cgemm_strided_batch(
+    cuMpSGEMM_handle_t handle, const cublasOperation_t op_A, const cublasOperation_t op_B,
+    const uint64_t m, const uint64_t n, const uint64_t k, const cuComplex *alpha,
+    const cuComplex *const a_dmem_ptr, const uint64_t lda, const uint64_t stridea,
+    const cuComplex *const b_dmem_ptr, const uint64_t ldb, const uint64_t strideb,
+    const cuComplex *beta, cuComplex *const c_dmem_ptr, const uint64_t ldc,
+    const uint64_t stridec, const uint64_t batch_count,
+    const cuMpSGEMM_compute_mode_t compute_mode) {
+  return cumpsgemm::gemm_stridedBatch<cuComplex>(handle, op_A, op_B, m, n, k, alpha, a_dmem_ptr,
+                                                 lda, stridea, b_dmem_ptr, ldb, strideb, beta,
+                                                 c_dmem_ptr, ldc, stridec, batch_count,
+                                                 compute_mode);
+}
+
+} // extern "C"

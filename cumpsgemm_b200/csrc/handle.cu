@@ -1,0 +1,127 @@
+// Handle life cycle, logging helpers and the mode-name table.
+//
+// Reference counterparts: src/handle.cu:7-52 (create / destroy / set_stream),
+// src/utils.hpp:5-42 (logging), src/cumpsgemm_cublas.cu:163-196 (mode names).
+#include "internal.hpp"
+
+#include <new>
+#include <string>
+
+namespace cumpsgemm_b200 {
+void configure_mode_buffer(cuMpSGEMM_handle *h);
+void init_flag_buffer(cuMpSGEMM_handle *h);
+
+bool env_flag(const char *name, bool default_value) {
+  const char *env = std::getenv(name);
+  if (env == nullptr) return default_value;
+  return std::string(env) != "0";
+}
+void log_info(const std::string &s) {
+  if (env_flag("CUMPSGEMM_INFO", false)) {
+    std::fprintf(stdout, "[cuMpSGEMM LOG] %s\n", s.c_str());
+    std::fflush(stdout);
+  }
+}
+void log_error(const std::string &s) {
+  if (env_flag("CUMPSGEMM_ERROR_LOG", true)) {
+    std::fprintf(stdout, "[cuMpSGEMM ERROR] %s\n", s.c_str());
+    std::fflush(stdout);
+  }
+}
+void log_warning(const std::string &s) {
+  if (env_flag("CUMPSGEMM_ERROR_LOG", false)) {
+    std::fprintf(stdout, "[cuMpSGEMM WARNING] %s\n", s.c_str());
+    std::fflush(stdout);
+  }
+}
+} // namespace cumpsgemm_b200
+
+using namespace cumpsgemm_b200;
+
+extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
+  if (handle == nullptr) return CUBLAS_STATUS_INVALID_VALUE;
+  cuMpSGEMM_handle *h = new (std::nothrow) cuMpSGEMM_handle;
+  if (h == nullptr) return CUBLAS_STATUS_ALLOC_FAILED;
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    delete h;
+    return CUBLAS_STATUS_NOT_INITIALIZED;
+  }
+  h->device = dev;
+  int sms = 0, cc_major = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+  h->num_sms = static_cast<unsigned>(sms);
+  if (cc_major != 10) {
+    log_error("this build contains sm_100a kernels only; device compute capability major is " +
+              std::to_string(cc_major));
+    delete h;
+    return CUBLAS_STATUS_ARCH_MISMATCH;
+  }
+
+  bool ok = true;
+  auto &es = h->exp_stats;
+  ok &= cudaMalloc(&es.dev_total, sizeof(unsigned long long) * es.buffer_length) == cudaSuccess;
+  ok &= cudaMalloc(&es.dev_underflow, sizeof(unsigned long long) * es.buffer_length) == cudaSuccess;
+  ok &= cudaMalloc(&es.dev_max, sizeof(float) * es.buffer_length) == cudaSuccess;
+  ok &= cudaMalloc(&es.dev_mode, sizeof(int) * es.buffer_length) == cudaSuccess;
+  ok &= cudaMalloc(&h->dyn_launch.flag_buffer, sizeof(int) * h->dyn_launch.flag_buffer_length) ==
+        cudaSuccess;
+  ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
+  ok &= cudaMalloc(&h->dev_status, sizeof(int)) == cudaSuccess;
+  if (!ok) {
+    cuMpSGEMM_destroy(h);
+    return CUBLAS_STATUS_ALLOC_FAILED;
+  }
+  cudaMemsetAsync(es.dev_total, 0, sizeof(unsigned long long) * es.buffer_length, h->cuda_stream);
+  cudaMemsetAsync(es.dev_underflow, 0, sizeof(unsigned long long) * es.buffer_length,
+                  h->cuda_stream);
+  cudaMemsetAsync(es.dev_max, 0, sizeof(float) * es.buffer_length, h->cuda_stream);
+  cudaMemsetAsync(es.dev_mode, 0, sizeof(int) * es.buffer_length, h->cuda_stream);
+  cudaMemsetAsync(h->dyn_launch.flag_buffer, 0, sizeof(int) * h->dyn_launch.flag_buffer_length,
+                  h->cuda_stream);
+  cudaMemsetAsync(h->dev_status, 0, sizeof(int), h->cuda_stream);
+  configure_mode_buffer(h);
+  init_flag_buffer(h);
+  if (cudaStreamSynchronize(h->cuda_stream) != cudaSuccess) {
+    cuMpSGEMM_destroy(h);
+    return CUBLAS_STATUS_EXECUTION_FAILED;
+  }
+  const char *ws_env = std::getenv("CUMPSGEMM_WORKSPACE_LIMIT_MB");
+  if (ws_env != nullptr) h->workspace_limit_bytes = std::strtoull(ws_env, nullptr, 10) << 20;
+  *handle = h;
+  return CUBLAS_STATUS_SUCCESS;
+}
+
+extern "C" cublasStatus_t cuMpSGEMM_destroy(cuMpSGEMM_handle_t handle) {
+  if (handle == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  DeviceGuard guard(handle->device);
+  cudaFree(handle->exp_stats.dev_total);
+  cudaFree(handle->exp_stats.dev_underflow);
+  cudaFree(handle->exp_stats.dev_max);
+  cudaFree(handle->exp_stats.dev_mode);
+  cudaFree(handle->dyn_launch.flag_buffer);
+  cudaFree(handle->dev_dyn_params);
+  cudaFree(handle->dev_status);
+  cudaFree(handle->workspace);
+  delete handle;
+  return CUBLAS_STATUS_SUCCESS;
+}
+
+extern "C" cublasStatus_t cuMpSGEMM_set_stream(cuMpSGEMM_handle_t handle,
+                                               const cudaStream_t cuda_stream) {
+  if (handle == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  handle->cuda_stream = cuda_stream;
+  return CUBLAS_STATUS_SUCCESS;
+}
+
+extern "C" const char *cuMpSGEMM_get_compute_mode_string(const cuMpSGEMM_compute_mode_t mode) {
+  static const char *const names[] = {
+      "CUBLAS",      "FP16TCEC",      "TF32TCEC", "FP16TC", "TF32TC",    "CUBLAS_SIMT",
+      "CUBLAS_FP16TC", "CUBLAS_TF32TC", "DRY_RUN",  "AUTO",   "UNDEFINED", "FP16TCEC_SCALING",
+      "FP32_SIMT"};
+  const int i = static_cast<int>(mode);
+  if (i < 0 || i >= static_cast<int>(sizeof(names) / sizeof(names[0]))) return "Unknown";
+  return names[i];
+}

@@ -1,0 +1,234 @@
+// Internal declarations shared by the translation units of libcumpsgemm.so.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <string>
+#include <unordered_map>
+#include <utility>
+
+#include <cuComplex.h>
+#include <cuda_runtime.h>
+#include <cumpsgemm/cumpsgemm.hpp>
+
+namespace cumpsgemm_b200 {
+
+// ---------------------------------------------------------------- logging
+// Same grammar and environment switches as the reference's src/utils.hpp:5-42:
+// "[cuMpSGEMM LOG] ..." when CUMPSGEMM_INFO is set and not "0";
+// "[cuMpSGEMM ERROR] ..." unless CUMPSGEMM_ERROR_LOG=0;
+// "[cuMpSGEMM WARNING] ..." only when CUMPSGEMM_ERROR_LOG is set and not "0".
+bool env_flag(const char *name, bool default_value);
+void log_info(const std::string &s);
+void log_error(const std::string &s);
+void log_warning(const std::string &s);
+
+// ---------------------------------------------------------------- flag word
+// Dynamic-launch flag word: bits [0,5) GEMM mode, bit 5 "scale B", bit 6
+// "scale A" (reference: src/dynamic_launch_utils.hpp:7-41).
+constexpr int kFlagModeMask = 0x1f;
+constexpr int kFlagScaleB = 0x20;
+constexpr int kFlagScaleA = 0x40;
+__host__ __device__ inline int flag_gemm_mode(int flag) { return flag & kFlagModeMask; }
+__host__ __device__ inline bool flag_scale_a(int flag) { return (flag & kFlagScaleA) != 0; }
+__host__ __device__ inline bool flag_scale_b(int flag) { return (flag & kFlagScaleB) != 0; }
+
+// Scaling target: operands are scaled so that their largest exponent becomes
+// 2^14 (reference: src/dynamic_scaling.cu:15).
+constexpr float kHalfExpMax = 16384.0f;
+
+// Per-call constants of the fused AUTO / FP16TCEC_SCALING pipeline, computed
+// on the device from a flag word and two statistics slots so that the host
+// never synchronises.
+struct DynParams {
+  float scale_a;   // multiply op(A) by this (exact power of two) before splitting
+  float scale_b;   // same for op(B)
+  float unscale_c; // multiply the product by this in the GEMM epilogue
+  int gemm_mode;   // CUMPSGEMM_FP16TCEC or CUMPSGEMM_TF32TCEC
+};
+
+// ---------------------------------------------------------------- profiler
+// Named accumulating timers (reference uses cutf's time_breakdown profiler:
+// src/exp_stats.cu:309-378).  start/stop synchronise the stream.
+struct Profiler {
+  struct Entry {
+    double sum_s = 0;
+    std::uint64_t n = 0;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+  };
+  std::unordered_map<std::string, Entry> entries;
+  void start(const std::string &name, cudaStream_t s);
+  void stop(const std::string &name, cudaStream_t s);
+  void clear();
+  ~Profiler();
+};
+
+struct ExpStatsState {
+  bool enabled = false;
+  unsigned long long *dev_total = nullptr;
+  unsigned long long *dev_underflow = nullptr;
+  int *dev_mode = nullptr;
+  float *dev_max = nullptr;
+  float ignore_threshold = 0.f;
+  float underflow_threshold = 1.f / 32768.f;
+  float underflow_tolerance_rate = 0.f;
+  std::uint32_t buffer_length = 10000;
+  std::uint32_t current_buffer_id = 1;
+  Profiler profiler;
+  bool profiling_enabled = false;
+};
+
+struct DynLaunchState {
+  unsigned flag_buffer_length = 10000;
+  unsigned current_buffer_id = 1;
+  int *flag_buffer = nullptr;
+  bool enabled = false;
+  unsigned enabled_id = 0;
+};
+
+} // namespace cumpsgemm_b200
+
+// The public opaque handle (reference: src/handle.hpp:7-29).
+struct cuMpSGEMM_handle {
+  int device = 0;
+  unsigned num_sms = 0;
+  cudaStream_t cuda_stream = 0;
+  cumpsgemm_b200::ExpStatsState exp_stats;
+  cumpsgemm_b200::DynLaunchState dyn_launch;
+
+  // Ring of DynParams records for fused scaling calls.
+  cumpsgemm_b200::DynParams *dev_dyn_params = nullptr;
+  unsigned dyn_params_length = 1024;
+  unsigned dyn_params_next = 0;
+
+  // Operand workspace: hi/lo panels of op(A) and op(B) in the K-major tile
+  // format the GEMM kernel reads through TMA.  Grown on demand.
+  void *workspace = nullptr;
+  std::size_t workspace_bytes = 0;
+  std::size_t workspace_limit_bytes = 0; // 0 = derive from free memory
+
+  // Device status word the GEMM kernel writes when a bounded wait gives up.
+  int *dev_status = nullptr;
+};
+
+namespace cumpsgemm_b200 {
+
+// RAII: make the handle's device current for the duration of a call.
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) {
+      cudaSetDevice(dev);
+      changed = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+// ---------------------------------------------------------------- operand split
+enum class SplitKind : int { fp16 = 0, tf32 = 1 };
+enum class Operand : int { A = 0, B = 1 };
+
+struct SplitArgs {
+  SplitKind kind;
+  Operand operand;
+  bool is_complex;
+  bool conjugate;      // op == C on complex input
+  bool src_k_contig;   // true: source element (r, kk) at [kk + r*ld]; false: [r + kk*ld]
+  std::uint64_t rows;  // logical rows of op(X): m for A, n for B (complex: complex elements)
+  std::uint64_t k;     // logical K (complex: complex elements)
+  const void *src;
+  std::uint64_t ld;     // in elements of the source type
+  std::uint64_t stride; // batch stride in elements of the source type
+  std::uint32_t batch;
+  void *panel;             // destination
+  std::uint32_t rows_pad;  // padded expanded rows (multiple of 64)
+  std::uint32_t k_pad;     // padded expanded K (multiple of 64)
+  bool with_lo;            // also write the lo panel
+  const DynParams *dyn;    // nullable: scale factor and gating
+};
+cudaError_t launch_split(const SplitArgs &a, cudaStream_t stream);
+
+// ---------------------------------------------------------------- TCEC GEMM
+struct TcecGemmArgs {
+  SplitKind kind;
+  bool error_correction;
+  std::uint32_t m, n;  // C extent in floats (complex: m counts re/im rows separately)
+  std::uint32_t k_pad;
+  std::uint32_t rows_pad_a, rows_pad_b;
+  std::uint32_t batch;
+  const void *panel_a;
+  const void *panel_b;
+  float *c;
+  std::uint64_t ldc;      // in floats
+  std::uint64_t stride_c; // in floats
+  float alpha_r, alpha_i, beta_r, beta_i;
+  bool is_complex;
+  const DynParams *dyn; // nullable
+  int tile_n;           // 256, 128 or 64
+  int *dev_status;
+};
+cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
+// Dynamic shared memory and stage count of a tile configuration (for tests/docs).
+int tcec_gemm_stages(int tile_n, bool error_correction);
+
+// ---------------------------------------------------------------- statistics & scaling
+// Stage-wise entry points so that a multi-GPU caller can all-reduce the slot
+// between stages; exp_stats_ext() below chains them.
+void exp_stats_init_slot(cuMpSGEMM_handle *h, unsigned id);
+template <class T>
+void exp_stats_stage1(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
+                      unsigned ld, unsigned batch, unsigned stride);
+void exp_stats_decide1(cuMpSGEMM_handle *h, unsigned id);
+template <class T>
+void exp_stats_stage2(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
+                      unsigned ld, unsigned batch, unsigned stride);
+void exp_stats_decide2(cuMpSGEMM_handle *h, unsigned id);
+template <class T>
+void exp_max_only(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
+                  unsigned ld, unsigned batch, unsigned stride);
+unsigned next_exp_stats_id(cuMpSGEMM_handle *h);
+unsigned next_dyn_launch_id(cuMpSGEMM_handle *h);
+
+enum class ScaleOp : int { scale_a, scale_b, scale_c, reset_a, reset_b };
+template <class T>
+void launch_scaling(cuMpSGEMM_handle *h, ScaleOp op, unsigned m, unsigned n, T *ptr, unsigned ld,
+                    unsigned batch, unsigned stride, unsigned stats_id_a, unsigned stats_id_b,
+                    unsigned flag_id);
+
+// Fill the next DynParams record from a flag slot and two statistics slots.
+DynParams *prepare_dyn_params(cuMpSGEMM_handle *h, unsigned flag_id, unsigned stats_id_a,
+                              unsigned stats_id_b);
+
+// ---------------------------------------------------------------- GEMM dispatch
+// Shared implementation behind gemm<T> / gemm_stridedBatch<T>.
+// `dyn` != nullptr selects the fused scaling path (scale in the split pass,
+// un-scale in the epilogue); `gate_by_flag` launches both kinds gated on
+// dyn->gemm_mode.
+template <class T>
+cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperation_t op_B,
+                             std::uint64_t m, std::uint64_t n, std::uint64_t k, const T *alpha,
+                             const T *a, std::uint64_t lda, std::uint64_t stridea, const T *b,
+                             std::uint64_t ldb, std::uint64_t strideb, const T *beta, T *c,
+                             std::uint64_t ldc, std::uint64_t stridec, std::uint64_t batch,
+                             cuMpSGEMM_compute_mode_t mode, const DynParams *dyn,
+                             unsigned *used_kernel_module_id);
+
+// Full AUTO / FP16TCEC_SCALING pipeline (statistics -> flag -> fused GEMM).
+// Does not modify A or B.
+template <class T>
+cublasStatus_t gemm_with_statistics(cuMpSGEMM_handle *h, cublasOperation_t op_A,
+                                    cublasOperation_t op_B, std::uint64_t m, std::uint64_t n,
+                                    std::uint64_t k, const T *alpha, const T *a, std::uint64_t lda,
+                                    std::uint64_t stridea, const T *b, std::uint64_t ldb,
+                                    std::uint64_t strideb, const T *beta, T *c, std::uint64_t ldc,
+                                    std::uint64_t stridec, std::uint64_t batch,
+                                    cuMpSGEMM_compute_mode_t mode, unsigned *stats_id_a_out,
+                                    unsigned *stats_id_b_out, unsigned *flag_id_out);
+
+} // namespace cumpsgemm_b200

@@ -1,0 +1,208 @@
+// Operand split pass: FP32 / complex64 column-major operand -> K-major hi/lo panels.
+//
+// Restates, as one HBM-bound pass per operand, the FP32 -> (hi, lo) split the
+// reference performs inside its fragment loads for every warp and every k-step
+// (src/device_tcec_wrapper.hpp:72-80 calling mtk::wmma::tcec::load_matrix_sync),
+// together with the operand addressing of its global->shared loaders
+// (src/dmem_accessor.hpp:8-170: op N/T/C, leading dimension, edge zero fill,
+// conjugation).
+//
+//   FP16:  hi = RN_fp16(v),  lo = RN_fp16((v - float(hi)) * 2^11)
+//   TF32:  hi = RNA_tf32(v), lo = RNA_tf32(v - hi)
+// where v = x * scale (scale is an exact power of two, 1 when no scaling).
+//
+// Panel layout (element type half or float):
+//   panel[((b * planes + z) * rows_pad + r) * k_pad + kk],  z = 0 (hi), 1 (lo)
+// rows_pad / k_pad are multiples of 64 and every padding element is written
+// as zero on every call, so the GEMM kernel needs no edge handling.
+//
+// Complex operands are expanded to real ones so that the GEMM kernel is a real
+// GEMM producing interleaved (re, im) rows of C:
+//   A' (2m x 2k): rows (2i, 2i+1), cols (2l, 2l+1) = [[re, -im], [im, re]] of a(i,l)
+//   B' (n x 2k):  row j, cols (2l, 2l+1) = (re, im) of b(l,j)
+// (a, b after op; op C conjugates).
+#include "internal.hpp"
+
+#include <cuda_fp16.h>
+
+namespace cumpsgemm_b200 {
+namespace {
+
+constexpr int TILE = 64;       // expanded rows and expanded K per CTA
+constexpr int THREADS = 256;
+
+__device__ __forceinline__ float to_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+struct SplitParams {
+  const float *src; // complex sources are addressed as pairs of floats
+  uint64_t ld, stride;
+  uint64_t rows, k; // logical source extent (complex elements for complex input)
+  void *panel;
+  uint32_t rows_pad, k_pad;
+  uint32_t planes; // 1 or 2
+  const DynParams *dyn;
+  int operand; // 0 = A, 1 = B
+  int conj;
+  int src_k_contig;
+};
+
+// MODE: 0 = real, 1 = complex A', 2 = complex B'
+template <int KIND, int MODE>
+__global__ void __launch_bounds__(THREADS) split_kernel(const SplitParams p) {
+  constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
+  float scale = 1.f;
+  if (p.dyn != nullptr) {
+    if (p.dyn->gemm_mode != MY_MODE) return;
+    scale = (p.operand == 0) ? p.dyn->scale_a : p.dyn->scale_b;
+  }
+
+  // Source tile in source coordinates; complex tiles store (re, im) in adjacent columns.
+  constexpr int SR = (MODE == 1) ? TILE / 2 : TILE; // source rows per tile
+  constexpr int SK = (MODE == 0) ? TILE : TILE / 2; // source k per tile
+  constexpr int ES = (MODE == 0) ? 1 : 2;           // floats per source element
+  __shared__ float tile[TILE][TILE + 1];
+
+  const uint32_t b = blockIdx.z;
+  const uint64_t r0 = static_cast<uint64_t>(blockIdx.y) * SR;
+  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * SK;
+  const float *src = p.src + static_cast<uint64_t>(b) * p.stride * ES;
+
+  // ---- phase 1: coalesced read along the source-contiguous dimension
+  for (int idx = threadIdx.x; idx < SR * SK; idx += THREADS) {
+    int r, kk;
+    if (p.src_k_contig) {
+      kk = idx % SK;
+      r = idx / SK;
+    } else {
+      r = idx % SR;
+      kk = idx / SR;
+    }
+    const uint64_t gr = r0 + r, gk = k0 + kk;
+    float re = 0.f, im = 0.f;
+    if (gr < p.rows && gk < p.k) {
+      const uint64_t off = p.src_k_contig ? (gk + gr * p.ld) : (gr + gk * p.ld);
+      if constexpr (ES == 1) {
+        re = src[off] * scale;
+      } else {
+        const float2 v = reinterpret_cast<const float2 *>(src)[off];
+        re = v.x * scale;
+        im = (p.conj ? -v.y : v.y) * scale;
+      }
+    }
+    if constexpr (ES == 1) {
+      tile[r][kk] = re;
+    } else {
+      tile[r][2 * kk] = re;
+      tile[r][2 * kk + 1] = im;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 2: each thread converts 8 consecutive expanded-K values of one expanded row
+  const uint64_t er0 = static_cast<uint64_t>(blockIdx.y) * TILE; // expanded row origin
+  const uint64_t ek0 = static_cast<uint64_t>(blockIdx.x) * TILE; // expanded K origin
+  const uint64_t plane_elems = static_cast<uint64_t>(p.rows_pad) * p.k_pad;
+#pragma unroll
+  for (int it = 0; it < TILE * TILE / (THREADS * 8); ++it) {
+    const int er = (threadIdx.x >> 3) + it * (THREADS >> 3);
+    const int ek = (threadIdx.x & 7) * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = ek + j;
+      if constexpr (MODE == 0 || MODE == 2) {
+        v[j] = tile[er][c];
+      } else {
+        const int sr = er >> 1;
+        const bool im_row = (er & 1) != 0;
+        const bool odd = (c & 1) != 0;
+        // [[re, -im], [im, re]]
+        const float x = tile[sr][(c & ~1) + ((im_row != odd) ? 1 : 0)];
+        v[j] = (!im_row && odd) ? -x : x;
+      }
+    }
+    const uint64_t out_off = (er0 + er) * p.k_pad + ek0 + ek;
+    if constexpr (KIND == 0) {
+      __align__(16) __half hi[8];
+      __align__(16) __half lo[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        hi[j] = __float2half_rn(v[j]);
+        lo[j] = __float2half_rn((v[j] - __half2float(hi[j])) * 2048.f);
+      }
+      __half *ph = reinterpret_cast<__half *>(p.panel) +
+                   static_cast<uint64_t>(b) * p.planes * plane_elems + out_off;
+      *reinterpret_cast<uint4 *>(ph) = *reinterpret_cast<const uint4 *>(hi);
+      if (p.planes == 2)
+        *reinterpret_cast<uint4 *>(ph + plane_elems) = *reinterpret_cast<const uint4 *>(lo);
+    } else {
+      __align__(16) float hi[8];
+      __align__(16) float lo[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        hi[j] = to_tf32(v[j]);
+        lo[j] = to_tf32(v[j] - hi[j]);
+      }
+      float *ph = reinterpret_cast<float *>(p.panel) +
+                  static_cast<uint64_t>(b) * p.planes * plane_elems + out_off;
+      reinterpret_cast<uint4 *>(ph)[0] = reinterpret_cast<const uint4 *>(hi)[0];
+      reinterpret_cast<uint4 *>(ph)[1] = reinterpret_cast<const uint4 *>(hi)[1];
+      if (p.planes == 2) {
+        reinterpret_cast<uint4 *>(ph + plane_elems)[0] = reinterpret_cast<const uint4 *>(lo)[0];
+        reinterpret_cast<uint4 *>(ph + plane_elems)[1] = reinterpret_cast<const uint4 *>(lo)[1];
+      }
+    }
+  }
+}
+
+template <int KIND, int MODE> cudaError_t launch(const SplitArgs &a, cudaStream_t stream) {
+  SplitParams p;
+  p.src = reinterpret_cast<const float *>(a.src);
+  p.ld = a.ld;
+  p.stride = a.stride;
+  p.rows = a.rows;
+  p.k = a.k;
+  p.panel = a.panel;
+  p.rows_pad = a.rows_pad;
+  p.k_pad = a.k_pad;
+  p.planes = a.with_lo ? 2u : 1u;
+  p.dyn = a.dyn;
+  p.operand = static_cast<int>(a.operand);
+  p.conj = a.conjugate ? 1 : 0;
+  p.src_k_contig = a.src_k_contig ? 1 : 0;
+  const dim3 grid(a.k_pad / TILE, a.rows_pad / TILE, a.batch);
+  if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidValue;
+  split_kernel<KIND, MODE><<<grid, THREADS, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+} // namespace
+
+cudaError_t launch_split(const SplitArgs &a, cudaStream_t stream) {
+  if ((a.rows_pad % TILE) != 0 || (a.k_pad % TILE) != 0) return cudaErrorInvalidValue;
+  const int mode = !a.is_complex ? 0 : (a.operand == Operand::A ? 1 : 2);
+  if (a.kind == SplitKind::fp16) {
+    switch (mode) {
+    case 0:
+      return launch<0, 0>(a, stream);
+    case 1:
+      return launch<0, 1>(a, stream);
+    default:
+      return launch<0, 2>(a, stream);
+    }
+  }
+  switch (mode) {
+  case 0:
+    return launch<1, 0>(a, stream);
+  case 1:
+    return launch<1, 1>(a, stream);
+  default:
+    return launch<1, 2>(a, stream);
+  }
+}
+
+} // namespace cumpsgemm_b200

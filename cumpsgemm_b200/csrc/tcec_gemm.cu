@@ -1,0 +1,428 @@
+// Error-corrected tensor-core GEMM for sm_100a.
+//
+// Replaces the reference's gemm_kernel / gemm_batchStrided_kernel /
+// gemm_atomic_kernel (src/cumpsgemm_kernel.cuh:468-585) and the fragment
+// arithmetic they call (src/device_tcec_wrapper.hpp:21-106).
+//
+// Inputs are the K-major hi/lo operand panels written by the split pass
+// (split_kernels.cu).  One CTA owns a 128 x BN tile of C:
+//   warp 0      : TMA producer (cp.async.bulk.tensor, no multicast)
+//   warp 1      : TMEM allocation + single-thread tcgen05.mma issue
+//   warps 4..11 : accumulator drain (tcgen05.ld), FP32 running sum in
+//                 registers, alpha/beta epilogue with direct coalesced stores
+// Per K stage (128 bytes of K per row = 64 FP16 or 32 TF32 values):
+//   D0  = Ahi * Bhi            (overwritten every stage, drained every stage
+//                               and added to the running sum with an FP32
+//                               round-to-nearest add outside the tensor core)
+//   D1 += Alo * Bhi + Ahi * Blo (stays in TMEM for the whole K loop)
+// result = sum(D0 drains) + D1 * lo_scale_inv   (2^-11 for FP16, 1 for TF32).
+// While the tensor core runs the two correction products of a stage the
+// epilogue warps drain D0 of the same stage, so D0 needs no double buffering
+// and the two accumulators fill the 512 TMEM columns at BN = 256.
+#include "internal.hpp"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace cumpsgemm_b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int ROW_BYTES = 128; // K extent of one stage in bytes = one 128-byte swizzle atom
+constexpr int NUM_THREADS = 384;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t D1_COL = 256;
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+template <int BN, bool EC> struct TileCfg {
+  static constexpr int A_TILE = BM * ROW_BYTES;
+  static constexpr int B_TILE = BN * ROW_BYTES;
+  static constexpr int STAGE_BYTES = (A_TILE + B_TILE) * (EC ? 2 : 1);
+  static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(STAGES >= 2, "need at least two stages");
+};
+
+struct KernelParams {
+  float *c;
+  uint64_t ldc;
+  uint64_t stride_c;
+  uint32_t m, n;
+  uint32_t k_blocks;
+  uint32_t tiles_m, tiles_n;
+  float alpha_r, alpha_i, beta_r, beta_i;
+  float lo_scale_inv;
+  int is_complex;
+  const DynParams *dyn;
+  int *status;
+};
+
+template <int KIND> __device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b,
+                                                           uint32_t idesc, uint32_t acc) {
+  if constexpr (KIND == 0) {
+    ptx::mma_f16_ss(d, a, b, idesc, acc);
+  } else {
+    ptx::mma_tf32_ss(d, a, b, idesc, acc);
+  }
+}
+
+template <int KIND, int BN, bool EC>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b, const KernelParams p) {
+  using Cfg = TileCfg<BN, EC>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
+  constexpr int BK = ROW_BYTES / ELEM_BYTES; // elements of K per stage
+  constexpr int K_STEPS = ROW_BYTES / 32;    // tcgen05.mma consumes 32 bytes of K per instruction
+  constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
+  constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, BM, BN);
+  constexpr int CPT = BN / 2; // accumulator columns per epilogue thread
+
+  // Gated launch: leave at once when the device-side decision picked the other kind.
+  if (p.dyn != nullptr && p.dyn->gemm_mode != MY_MODE) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + STAGES;
+  uint64_t *d0_full = bars + 2 * STAGES;
+  uint64_t *d0_empty = bars + 2 * STAGES + 1;
+  uint64_t *d1_full = bars + 2 * STAGES + 2;
+  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- tile coordinates: grouped raster so that concurrently resident CTAs
+  //      share A and B panels in L2
+  const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
+  const uint32_t batch_id = blockIdx.x / tiles_per_batch;
+  const uint32_t t = blockIdx.x - batch_id * tiles_per_batch;
+  constexpr uint32_t GROUP_M = 16;
+  const uint32_t tiles_in_group = GROUP_M * p.tiles_n;
+  const uint32_t group_id = t / tiles_in_group;
+  const uint32_t first_m = group_id * GROUP_M;
+  const uint32_t group_rows = min(p.tiles_m - first_m, GROUP_M);
+  const uint32_t in_group = t - group_id * tiles_in_group;
+  const uint32_t tile_m = first_m + in_group % group_rows;
+  const uint32_t tile_n = in_group / group_rows;
+  const int m0 = static_cast<int>(tile_m * BM);
+  const int n0 = static_cast<int>(tile_n * BN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(d0_full), 1);
+    ptx::mbar_init(ptx::smem_u32(d0_empty), NUM_EPI_WARPS);
+    ptx::mbar_init(ptx::smem_u32(d1_full), 1);
+    *abort_flag = 0;
+    ptx::mbar_init_fence();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_base_ptr), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_ptr;
+  const uint32_t k_blocks = p.k_blocks;
+
+  if (warp == 0) {
+    // ================================================================ TMA producer
+    if (lane == 0) {
+      const int za = static_cast<int>(batch_id * (EC ? 2u : 1u));
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
+                            ptx::kErrWaitEmpty))
+          break;
+        const uint32_t fb = ptx::smem_u32(&full_bar[s]);
+        ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
+        uint8_t *st = smem + s * Cfg::STAGE_BYTES;
+        const int kc = static_cast<int>(kb * BK);
+        ptx::tma_load_3d(ptx::smem_u32(st), &map_a, fb, kc, m0, za);
+        if constexpr (EC) {
+          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_a, fb, kc, m0, za + 1);
+          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE), &map_b, fb, kc, n0, za);
+          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE + Cfg::B_TILE), &map_b, fb, kc, n0,
+                           za + 1);
+        } else {
+          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_b, fb, kc, n0, za);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer
+    if (lane == 0) {
+      const uint32_t d0 = tmem_base;
+      const uint32_t d1 = tmem_base + D1_COL;
+      bool ok = true;
+      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const uint32_t s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                            ptx::kErrWaitFull);
+        if (!ok) break;
+        // D0 of the previous stage must have been drained before it is overwritten.
+        ok = ptx::mbar_wait(ptx::smem_u32(d0_empty), (kb & 1u) ^ 1u, abort_flag, p.status,
+                            ptx::kErrWaitD0Empty);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t st = ptx::smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t a_hi = ptx::make_kmajor_desc<ROW_BYTES>(st);
+        const uint64_t a_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + Cfg::A_TILE);
+        const uint64_t b_hi =
+            ptx::make_kmajor_desc<ROW_BYTES>(st + (EC ? 2 : 1) * Cfg::A_TILE);
+        const uint64_t b_lo =
+            ptx::make_kmajor_desc<ROW_BYTES>(st + 2 * Cfg::A_TILE + Cfg::B_TILE);
+#pragma unroll
+        for (int ks = 0; ks < K_STEPS; ++ks) {
+          // advancing K by 32 bytes inside the swizzle atom = +2 in the address field
+          mma_ss<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC, ks > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(ptx::smem_u32(d0_full));
+        if constexpr (EC) {
+#pragma unroll
+          for (int ks = 0; ks < K_STEPS; ++ks) {
+            mma_ss<KIND>(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < K_STEPS; ++ks) {
+            mma_ss<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
+          }
+        }
+        ptx::tc_commit(ptx::smem_u32(&empty_bar[s]));
+      }
+      if (ok) ptx::tc_commit(ptx::smem_u32(d1_full));
+    }
+  } else if (warp >= 4) {
+    // ================================================================ drain + epilogue
+    const uint32_t quarter = static_cast<uint32_t>(warp & 3);      // TMEM lanes [32q, 32q+32)
+    const uint32_t half = static_cast<uint32_t>((warp - 4) >> 2);  // column half of the tile
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const uint32_t col_base = half * CPT;
+
+    float acc[CPT];
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
+
+    bool ok = true;
+    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      ok = ptx::mbar_wait(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
+                          ptx::kErrWaitD0Full);
+      if (!ok) break;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int pc = 0; pc < CPT / 32; ++pc) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + col_base + pc * 32, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[pc * 32 + i] += __uint_as_float(v[i]);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(d0_empty));
+    }
+
+    if (ok && EC) {
+      ok = ptx::mbar_wait(ptx::smem_u32(d1_full), 0u, abort_flag, p.status, ptx::kErrWaitD1Full);
+      if (ok) {
+        ptx::tc_fence_after();
+        const float lsi = p.lo_scale_inv;
+#pragma unroll
+        for (int pc = 0; pc < CPT / 32; ++pc) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + D1_COL + lane_addr + col_base + pc * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[pc * 32 + i] = fmaf(__uint_as_float(v[i]), lsi, acc[pc * 32 + i]);
+        }
+      }
+    }
+
+    if (ok) {
+      // C(row, col) = alpha * acc + beta * C(row, col); lanes hold consecutive rows of a
+      // column-major C, so each warp store covers 128 contiguous bytes.
+      const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
+      const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
+      const float br = p.beta_r, bi = p.beta_i;
+      const bool read_c = (br != 0.f) || (bi != 0.f);
+      const uint32_t row = static_cast<uint32_t>(m0) + quarter * 32u + static_cast<uint32_t>(lane);
+      const bool row_ok = row < p.m;
+      float *cbase = p.c + static_cast<uint64_t>(batch_id) * p.stride_c + row;
+      const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) {
+        const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i);
+        if (col < p.n) { // uniform over the warp
+          float *cp = cbase + static_cast<uint64_t>(col) * p.ldc;
+          float old = 0.f;
+          if (read_c && row_ok) old = *cp;
+          float out;
+          if (p.is_complex) {
+            const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
+            const float old_o = __shfl_xor_sync(0xffffffffu, old, 1);
+            out = ar * acc[i] + sgn * ai * acc_o;
+            if (read_c) out += br * old + sgn * bi * old_o;
+          } else {
+            out = ar * acc[i];
+            if (read_c) out = fmaf(br, old, out);
+          }
+          if (row_ok) *cp = out;
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up.  Give copies that may still be in flight time to land in
+    // this CTA's shared memory before it is released.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {BK, box_rows, 1}, 128-byte swizzle.
+bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_t k_pad,
+                    uint32_t rows_pad, uint32_t planes, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const uint32_t es = (kind == SplitKind::fp16) ? 2u : 4u;
+  const cuuint64_t dims[3] = {k_pad, rows_pad, planes};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k_pad) * es,
+                                 static_cast<cuuint64_t>(k_pad) * es * rows_pad};
+  const cuuint32_t box[3] = {ROW_BYTES / es, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      (kind == SplitKind::fp16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUresult r =
+      fn(map, dt, 3, const_cast<void *>(panel), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int KIND, int BN, bool EC>
+cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
+  using Cfg = TileCfg<BN, EC>;
+  auto kernel = tcec_gemm_kernel<KIND, BN, EC>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const uint32_t planes = a.batch * (EC ? 2u : 1u);
+  CUtensorMap map_a, map_b;
+  if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, BM) ||
+      !make_panel_map(&map_b, a.kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, BN)) {
+    return cudaErrorInvalidValue;
+  }
+  KernelParams p;
+  p.c = a.c;
+  p.ldc = a.ldc;
+  p.stride_c = a.stride_c;
+  p.m = a.m;
+  p.n = a.n;
+  const uint32_t es = (a.kind == SplitKind::fp16) ? 2u : 4u;
+  p.k_blocks = a.k_pad / (ROW_BYTES / es);
+  p.tiles_m = (a.m + BM - 1) / BM;
+  p.tiles_n = (a.n + BN - 1) / BN;
+  p.alpha_r = a.alpha_r;
+  p.alpha_i = a.alpha_i;
+  p.beta_r = a.beta_r;
+  p.beta_i = a.beta_i;
+  p.lo_scale_inv = (a.kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
+  p.is_complex = a.is_complex ? 1 : 0;
+  p.dyn = a.dyn;
+  p.status = a.dev_status;
+  const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
+  if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
+  kernel<<<static_cast<unsigned>(grid), NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return cudaGetLastError();
+}
+
+template <int KIND, bool EC> cudaError_t launch_by_tile(const TcecGemmArgs &a, cudaStream_t s) {
+  switch (a.tile_n) {
+  case 256:
+    return launch_variant<KIND, 256, EC>(a, s);
+  case 128:
+    return launch_variant<KIND, 128, EC>(a, s);
+  case 64:
+    return launch_variant<KIND, 64, EC>(a, s);
+  default:
+    return cudaErrorInvalidValue;
+  }
+}
+
+} // namespace
+
+cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream) {
+  if (a.kind == SplitKind::fp16) {
+    return a.error_correction ? launch_by_tile<0, true>(a, stream)
+                              : launch_by_tile<0, false>(a, stream);
+  }
+  return a.error_correction ? launch_by_tile<1, true>(a, stream)
+                            : launch_by_tile<1, false>(a, stream);
+}
+
+int tcec_gemm_stages(int tile_n, bool ec) {
+  switch (tile_n) {
+  case 256:
+    return ec ? TileCfg<256, true>::STAGES : TileCfg<256, false>::STAGES;
+  case 128:
+    return ec ? TileCfg<128, true>::STAGES : TileCfg<128, false>::STAGES;
+  case 64:
+    return ec ? TileCfg<64, true>::STAGES : TileCfg<64, false>::STAGES;
+  default:
+    return 0;
+  }
+}
+
+} // namespace cumpsgemm_b200

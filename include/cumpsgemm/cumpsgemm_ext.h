@@ -1,0 +1,200 @@
+/* Plain-C entry points for the parts of the reference API that exist only as
+ * C++ (namespace cumpsgemm, include/cumpsgemm/cumpsgemm.hpp:45-129, and
+ * namespace cumpsgemm::hijack_control, include/cumpsgemm/hijack_control.hpp:7-34),
+ * so that ctypes / cgo / JNI style bindings can reach them without C++ name
+ * mangling.  Suffix _s = float, _c = cuComplex.  Every function forwards to
+ * the C++ function named in its comment; argument meaning is identical.
+ *
+ * The last section adds what a multi-GPU caller needs to make the AUTO /
+ * FP16TCEC_SCALING decisions global across ranks; it has no counterpart in
+ * the reference, which is single-GPU.
+ */
+#ifndef CUMPSGEMM_B200_CUMPSGEMM_EXT_H
+#define CUMPSGEMM_B200_CUMPSGEMM_EXT_H
+#include "cumpsgemm.h"
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- exponent statistics ------------------------------------------------ */
+/* cumpsgemm::exp_stats_ext<T>  (reference: src/exp_stats.cu:502-525) */
+unsigned cuMpSGEMM_exp_stats_ext_s(cuMpSGEMM_handle_t handle, unsigned m, unsigned n,
+                                   const float *ptr, unsigned ld, unsigned batch_size,
+                                   unsigned stride);
+unsigned cuMpSGEMM_exp_stats_ext_c(cuMpSGEMM_handle_t handle, unsigned m, unsigned n,
+                                   const cuComplex *ptr, unsigned ld, unsigned batch_size,
+                                   unsigned stride);
+/* cumpsgemm::exp_max_ext<T>  (reference: src/exp_stats.cu:534-557) */
+unsigned cuMpSGEMM_exp_max_ext_s(cuMpSGEMM_handle_t handle, unsigned m, unsigned n,
+                                 const float *ptr, unsigned ld, unsigned batch_size,
+                                 unsigned stride);
+unsigned cuMpSGEMM_exp_max_ext_c(cuMpSGEMM_handle_t handle, unsigned m, unsigned n,
+                                 const cuComplex *ptr, unsigned ld, unsigned batch_size,
+                                 unsigned stride);
+/* cumpsgemm::get_exp_stats  (reference: src/exp_stats.cu:615-629).  Synchronises. */
+void cuMpSGEMM_get_exp_stats(cuMpSGEMM_handle_t handle, unsigned buffer_id,
+                             size_t *underflow_count, size_t *total_count);
+/* cumpsgemm::get_current_exp_stats_buffer_id / reset_exp_stats_buffer_id */
+unsigned cuMpSGEMM_get_current_exp_stats_buffer_id(cuMpSGEMM_handle_t handle);
+void cuMpSGEMM_reset_exp_stats_buffer_id(cuMpSGEMM_handle_t handle);
+/* cumpsgemm::set_exp_stats_params  (reference: src/exp_stats.cu:631-638) */
+void cuMpSGEMM_set_exp_stats_params(cuMpSGEMM_handle_t handle, float ignore_threshold,
+                                    float underflow_threshold, float underflow_ratio_tolerance);
+/* cumpsgemm::enable_exp_stats / disable_exp_stats */
+void cuMpSGEMM_enable_exp_stats(cuMpSGEMM_handle_t handle);
+void cuMpSGEMM_disable_exp_stats(cuMpSGEMM_handle_t handle);
+/* cumpsgemm::get_max_exp  (reference: src/dynamic_scaling.cu:352-361).  Synchronises. */
+float cuMpSGEMM_get_max_exp(cuMpSGEMM_handle_t handle, unsigned buffer_id);
+/* cumpsgemm::get_exp_stats_compute_mode_level  (reference: src/exp_stats.cu:675-683) */
+int cuMpSGEMM_get_exp_stats_compute_mode_level(cuMpSGEMM_handle_t handle, unsigned buffer_id);
+
+/* ---- dynamic scaling (reference: src/dynamic_scaling.cu:227-350) --------- */
+void cuMpSGEMM_scale_A_s(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                         unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                         float *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_scale_A_c(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                         unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                         cuComplex *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_scale_B_s(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                         unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                         float *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_scale_B_c(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                         unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                         cuComplex *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_scale_C_s(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_A_id,
+                         unsigned exp_stats_buffer_B_id, unsigned dynamic_launch_flag_buffer_id,
+                         unsigned m, unsigned n, float *ptr, unsigned ld, unsigned batch_size,
+                         unsigned stride);
+void cuMpSGEMM_scale_C_c(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_A_id,
+                         unsigned exp_stats_buffer_B_id, unsigned dynamic_launch_flag_buffer_id,
+                         unsigned m, unsigned n, cuComplex *ptr, unsigned ld, unsigned batch_size,
+                         unsigned stride);
+void cuMpSGEMM_reset_scale_A_s(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                               unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                               float *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_reset_scale_A_c(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                               unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                               cuComplex *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_reset_scale_B_s(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                               unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                               float *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+void cuMpSGEMM_reset_scale_B_c(cuMpSGEMM_handle_t handle, unsigned exp_stats_buffer_id,
+                               unsigned dynamic_launch_flag_buffer_id, unsigned m, unsigned n,
+                               cuComplex *ptr, unsigned ld, unsigned batch_size, unsigned stride);
+
+/* ---- dynamic launch (reference: src/dynamic_launch.cu:36-70,
+ *      src/cumpsgemm.cu:776-812) ------------------------------------------ */
+unsigned cuMpSGEMM_get_current_dynamic_launch_buffer_id(cuMpSGEMM_handle_t handle);
+unsigned cuMpSGEMM_get_next_dynamic_launch_buffer_id(cuMpSGEMM_handle_t handle);
+int cuMpSGEMM_get_dynamic_launch_gemm_compute_mode(cuMpSGEMM_handle_t handle, unsigned buffer_id);
+void cuMpSGEMM_get_dynamic_launch_scaling_mode_AB(cuMpSGEMM_handle_t handle, unsigned buffer_id,
+                                                  int *scale_A, int *scale_B);
+void cuMpSGEMM_set_dynamic_launch_buffer_by_exp_stats(cuMpSGEMM_handle_t handle,
+                                                      unsigned dynamic_launch_buffer_id,
+                                                      unsigned A_exp_stats_buffer_id,
+                                                      unsigned B_exp_stats_buffer_id);
+/* cumpsgemm::dynamic_launch::set_/unset_dynamic_launch_flag_buffer_id
+ * (reference: src/dynamic_launch.cu:60-70): selects the flag slot a following
+ * gemm(..., CUMPSGEMM_AUTO) call is gated by. */
+void cuMpSGEMM_set_dynamic_launch_flag_buffer_id(cuMpSGEMM_handle_t handle, unsigned id);
+void cuMpSGEMM_unset_dynamic_launch_flag_buffer_id(cuMpSGEMM_handle_t handle);
+
+/* ---- timers (reference: src/cumpsgemm.cu:814-849) ------------------------ */
+void cuMpSGEMM_enable_exp_stats_profiling(cuMpSGEMM_handle_t handle);
+void cuMpSGEMM_disable_exp_stats_profiling(cuMpSGEMM_handle_t handle);
+void cuMpSGEMM_reset_exp_stats_profiling(cuMpSGEMM_handle_t handle);
+void cuMpSGEMM_print_exp_stats_profiling(cuMpSGEMM_handle_t handle, unsigned csv);
+/* cumpsgemm::debug::get_exp_stats_profiling_result for one timer name; returns 0 when the
+ * timer never ran. */
+int cuMpSGEMM_get_exp_stats_profiling_result(cuMpSGEMM_handle_t handle, const char *name,
+                                             double *time_sum_s, unsigned long long *n);
+
+/* ---- gemm variants reporting the tile configuration used ----------------- */
+/* cumpsgemm::gemm<T> / gemm_stridedBatch<T> with their used_kernel_module_id out-parameter
+ * (reference: include/cumpsgemm/cumpsgemm.hpp:18-43). */
+cublasStatus_t cuMpSGEMM_sgemm_module(
+    cuMpSGEMM_handle_t handle, cublasOperation_t op_A, cublasOperation_t op_B, uint64_t m,
+    uint64_t n, uint64_t k, const float *alpha, const float *a, uint64_t lda, const float *b,
+    uint64_t ldb, const float *beta, float *c, uint64_t ldc, cuMpSGEMM_compute_mode_t mode,
+    unsigned *used_kernel_module_id);
+
+/* ---- kernel status -------------------------------------------------------- */
+/* Every wait inside the GEMM kernel is bounded; a wait that gives up records a non-zero
+ * code in a device word.  This call synchronises the handle's stream, returns the word and
+ * clears it.  0 = no error. */
+int cuMpSGEMM_get_kernel_status(cuMpSGEMM_handle_t handle);
+/* Cap (bytes) for the operand workspace a strided-batch call may use at once; batches beyond
+ * it are processed in chunks.  0 restores the default (8 GiB). */
+void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
+
+/* ---- interception-layer control (cumpsgemm::hijack_control, reference:
+ *      src/cumpsgemm_cublas.cu:1189-1271) ---------------------------------- */
+cuMpSGEMM_handle_t cuMpSGEMM_hijack_get_internal_global_handle(void);
+/* returns 0, or 1 if the mode is rejected (CUMPSGEMM_FP32_SIMT; the C++ function throws) */
+int cuMpSGEMM_hijack_set_compute_mode(int mode);
+void cuMpSGEMM_hijack_unset_compute_mode(void);
+void cuMpSGEMM_hijack_reset_exp_stats_buffer_id(void);
+void cuMpSGEMM_hijack_set_exp_stats_params(float ignore_threshold, float underflow_threshold,
+                                           float underflow_tolerance_rate);
+void cuMpSGEMM_hijack_enable_restoring_AB_after_scaling(void);
+void cuMpSGEMM_hijack_disable_restoring_AB_after_scaling(void);
+/* copies at most size-1 characters and NUL-terminates; returns the full length */
+size_t cuMpSGEMM_hijack_get_last_called_function_str(char *buf, size_t size);
+void cuMpSGEMM_hijack_clear_last_called_function_str(void);
+int cuMpSGEMM_hijack_is_library_loaded(void);
+/* C callback form of hijack_control::set_control_function; NULL unsets. */
+typedef int (*cuMpSGEMM_control_function_c_t)(int op_A, int op_B, unsigned m, unsigned n,
+                                              unsigned k);
+void cuMpSGEMM_hijack_set_control_function(cuMpSGEMM_control_function_c_t fn);
+/* The mode the rule chain would pick for a call (control function, then
+ * libcumpsgemm_rule.so, then the built-in default).  Reference:
+ * cuMpSGEMM_get_compute_mode_internal, src/cumpsgemm_cublas.cu:198-220. */
+cuMpSGEMM_compute_mode_t cuMpSGEMM_get_compute_mode_internal(
+    const char *const func_name, cublasHandle_t const cublas_handle,
+    const cublasOperation_t op_A, const cublasOperation_t op_B, const unsigned m,
+    const unsigned n, const unsigned k);
+
+/* ---- multi-GPU support: staged statistics and a GEMM that takes decided
+ *      statistics slots.  No counterpart in the reference. ------------------ */
+/* Take the next statistics slot and zero it. */
+unsigned cuMpSGEMM_exp_stats_begin(cuMpSGEMM_handle_t handle);
+/* stage: 1 = max exponent + absolute-threshold counts, 2 = relative-threshold recount
+ * (runs on the device only if decision 1 left the slot undecided),
+ * 3 = max exponent only. */
+void cuMpSGEMM_exp_stats_stage_s(cuMpSGEMM_handle_t handle, int stage, unsigned id, unsigned m,
+                                 unsigned n, const float *ptr, unsigned ld, unsigned batch_size,
+                                 unsigned stride);
+void cuMpSGEMM_exp_stats_stage_c(cuMpSGEMM_handle_t handle, int stage, unsigned id, unsigned m,
+                                 unsigned n, const cuComplex *ptr, unsigned ld,
+                                 unsigned batch_size, unsigned stride);
+/* decision: 1 or 2 (reference: src/exp_stats.cu:169-184, :277-293). */
+void cuMpSGEMM_exp_stats_decide(cuMpSGEMM_handle_t handle, int decision, unsigned id);
+/* Copy a slot to / from four 64-bit words in device memory:
+ * {max exponent bits, total, underflow, mode}.  Ranks all-reduce words 0 (max) and
+ * 1..2 (sum) between a stage and its decision. */
+void cuMpSGEMM_exp_stats_export(cuMpSGEMM_handle_t handle, unsigned id,
+                                unsigned long long *dev_words4);
+void cuMpSGEMM_exp_stats_import(cuMpSGEMM_handle_t handle, unsigned id,
+                                const unsigned long long *dev_words4);
+/* Strided-batch GEMM whose scaling / kind selection comes from statistics slots that were
+ * already decided (by the calls above).  mode is CUMPSGEMM_AUTO (flag slot derived from the
+ * two statistics slots) or CUMPSGEMM_FP16TCEC_SCALING (both operands scaled). */
+cublasStatus_t cuMpSGEMM_sgemm_strided_batch_with_stats(
+    cuMpSGEMM_handle_t handle, cublasOperation_t op_A, cublasOperation_t op_B, uint64_t m,
+    uint64_t n, uint64_t k, const float *alpha, const float *a, uint64_t lda, uint64_t stridea,
+    const float *b, uint64_t ldb, uint64_t strideb, const float *beta, float *c, uint64_t ldc,
+    uint64_t stridec, uint64_t batch_count, cuMpSGEMM_compute_mode_t mode, unsigned stats_id_a,
+    unsigned stats_id_b);
+cublasStatus_t cuMpSGEMM_cgemm_strided_batch_with_stats(
+    cuMpSGEMM_handle_t handle, cublasOperation_t op_A, cublasOperation_t op_B, uint64_t m,
+    uint64_t n, uint64_t k, const cuComplex *alpha, const cuComplex *a, uint64_t lda,
+    uint64_t stridea, const cuComplex *b, uint64_t ldb, uint64_t strideb, const cuComplex *beta,
+    cuComplex *c, uint64_t ldc, uint64_t stridec, uint64_t batch_count,
+    cuMpSGEMM_compute_mode_t mode, unsigned stats_id_a, unsigned stats_id_b);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
