@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the TCEC GEMM hot path.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N --steps K ...  # CPU arm (see below)
+
+One step = one C = alpha*A*B + beta*C call through the cuMpSGEMM C ABI in
+FP16TCEC mode on a seeded synthetic m = n = k = 16384 problem (A, B uniform(-1,1)
+times 2^e with e uniform over the integers [-8, 8], C uniform(-1,1), alpha = 1,
+beta = 0.5).  The metric is effective TFLOP/s = 2*m*n*k / t.
+
+N = 1 : the whole problem on one GPU.
+N > 1 : one process per GPU (torchrun).  C and B are split by column blocks with
+        16384 columns per rank (weak scaling: n = 16384 * N), A (1 GiB) is
+        broadcast from rank 0 with NCCL inside every step, then every rank runs
+        its block with no further communication.
+
+The JSON line also carries
+  roofline     : the GEMM kernel's own device time (CUDA events on the launching
+                 stream around the kernel, recorded by the library) against the
+                 emulation roofline = measured dense 16-bit tensor peak / 3 MMAs;
+  e2e          : the same metric with A, B, C in pinned host memory, host<->device
+                 copies inside the timed region;
+  cpu_baseline : FP32 host GEMM (the oracle's register-blocked kernel, all host
+                 cores) on a bounded column slice of the same problem (rank 0,
+                 N = 1 only).
+
+`--impl reference`: the reference's own kernels target sm_80/sm_86 and depend on
+three absent submodules, so there is no reference GPU arm; the CPU arm times the
+FP32 host GEMM on a bounded column slice per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "effective TFLOP/s of FP16TCEC SGEMM at N=16384"
+UNIT = "TFLOP/s"
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"burst": float(d["bf16_tflops"]), "sustained": float(d["bf16_tflops_sustained"]),
+                "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def make_inputs_device(torch, n_rows, n_cols_b, k, seed, device):
+    """Seeded uniform(-1,1) * 2^e, e in [-8, 8]; C0 uniform(-1,1).  Column-major flat storage."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+
+    def scaled(count):
+        u = torch.rand(count, device=device, generator=g) * 2 - 1
+        e = torch.randint(-8, 9, (count,), device=device, generator=g, dtype=torch.int32)
+        return torch.ldexp(u, e)
+
+    a = scaled(n_rows * k)
+    b = scaled(k * n_cols_b)
+    c = torch.rand(n_rows * n_cols_b, device=device, generator=g) * 2 - 1
+    return a, b, c
+
+
+def cpu_gemm_sample(n_full: int, target_seconds: float, seed: int = 1):
+    """Times the oracle's FP32 host GEMM on a column slice of the n_full^3 problem.
+    Returns (TFLOP/s, seconds, columns)."""
+    import numpy as np
+    from oracle import oracle as orc
+
+    m = k = n_full
+    rng = orc.rng(seed)
+    a = (rng.uniform(-1, 1, size=m * k).astype(np.float32))
+    cols_cal = 48
+    b = rng.uniform(-1, 1, size=k * cols_cal).astype(np.float32)
+    c = np.zeros(m * cols_cal, dtype=np.float32)
+    t0 = time.perf_counter()
+    orc.gemm_f32(0, 0, m, cols_cal, k, 1.0, a, m, b, k, 0.0, c, m)
+    t_cal = time.perf_counter() - t0          # includes packing A once
+    t0 = time.perf_counter()
+    orc.gemm_f32(0, 0, m, 2 * cols_cal, k, 1.0, a, m, np.concatenate([b, b]), k, 0.0,
+                 np.zeros(m * 2 * cols_cal, dtype=np.float32), m)
+    t_cal2 = time.perf_counter() - t0
+    per_col = max((t_cal2 - t_cal) / cols_cal, 1e-6)
+    fixed = max(t_cal - per_col * cols_cal, 0.0)
+    cols = int(max(cols_cal, min(n_full, (target_seconds - fixed) / per_col)))
+    cols = max(6, cols // 6 * 6)
+    b = rng.uniform(-1, 1, size=k * cols).astype(np.float32)
+    c = np.zeros(m * cols, dtype=np.float32)
+    t0 = time.perf_counter()
+    orc.gemm_f32(0, 0, m, cols, k, 1.0, a, m, b, k, 0.0, c, m)
+    dt = time.perf_counter() - t0
+    return 2.0 * m * cols * k / dt / 1e12, dt, cols
+
+
+def run_reference(args, rank, world):
+    """CPU arm: FP32 host GEMM on the box's host cores, bounded sample per step."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+
+    n_full = args.n
+    m = k = n_full
+    cores = host_cores()
+    rng = orc.rng(1)
+    a = rng.uniform(-1, 1, size=m * k).astype(np.float32)
+    # size one step at about 4 s
+    tf, dt, cols = cpu_gemm_sample(n_full, 4.0)
+    b = rng.uniform(-1, 1, size=k * cols).astype(np.float32)
+    c = rng.uniform(-1, 1, size=m * cols).astype(np.float32)
+    for _ in range(args.warmup):
+        orc.gemm_f32(0, 0, m, cols, k, 1.0, a, m, b, k, 0.5, c, m)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.gemm_f32(0, 0, m, cols, k, 1.0, a, m, b, k, 0.5, c, m)
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    value = 2.0 * m * cols * k * args.steps / dt / 1e12
+    sample = (f"FP32 host GEMM (oracle port of the path's arithmetic in plain FP32), m=k={n_full}, "
+              f"{cols} of {n_full} columns per step, all {cores} host threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"FP32 SGEMM m=k={n_full}, column slice n={cols}, alpha=1, beta=0.5",
+                   "note": "the reference's GPU kernels (sm_80/sm_86, absent submodules) cannot "
+                           "be built; this arm is the CPU restatement on host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, local_rank, world):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=device)
+
+    from cumpsgemm_b200 import api
+    from cumpsgemm_b200.sharded import ShardedGemm
+
+    mode = api.ComputeMode[args.mode]
+    n = args.n
+    m = k = n
+    n_local = n                      # weak scaling: every rank owns n columns of C
+    handle = api.Handle()
+    handle.use_current_torch_stream()
+    sharded = ShardedGemm(handle)
+
+    a, b, c = make_inputs_device(torch, m, n_local, k, seed=1234 + rank, device=device)
+    if world > 1 and rank != 0:
+        a.zero_()                    # content arrives through the broadcast in every step
+
+    def step():
+        if world > 1:
+            sharded.gemm_column_block(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c, m, mode,
+                                      root=0, broadcast_A=True)
+        else:
+            handle.gemm(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c, m, mode)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    handle.set_kernel_timing(True)
+    handle.get_kernel_timing()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    groups, split_ms, gemm_ms = handle.get_kernel_timing()
+    handle.set_kernel_timing(False)
+    kstatus = handle.kernel_status()
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    flops_per_step = 2.0 * m * (n_local * world) * k
+    value = flops_per_step / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM kernel), this rank
+    peaks = read_peaks()
+    long_run = elapsed_ms > 2000.0
+    peak_dense = peaks["sustained"] if long_run else peaks["burst"]
+    mma_per_product = 3 if mode in (api.ComputeMode.FP16TCEC, api.ComputeMode.FP16TCEC_SCALING,
+                                    api.ComputeMode.AUTO) else (3 if mode == api.ComputeMode.TF32TCEC
+                                                                else 1)
+    tf32 = mode in (api.ComputeMode.TF32TCEC, api.ComputeMode.TF32TC)
+    peak = peak_dense / (2.0 if tf32 else 1.0) / mma_per_product
+    gemm_ms_avg = gemm_ms / max(groups, 1)
+    achieved = 2.0 * m * n_local * k / (gemm_ms_avg * 1e-3) / 1e12 if gemm_ms_avg > 0 else 0.0
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak if peak else None, "traffic": None,
+        "kernel": "tcec_gemm_kernel (tcgen05, 128x256 tile)",
+        "kernel_ms": gemm_ms_avg, "split_pass_ms": split_ms / max(groups, 1),
+        "peak_source": f"{peaks['source']} dense 16-bit tensor peak "
+                       f"({'sustained' if long_run else 'burst'}) {peak_dense} TFLOP/s / "
+                       f"{'2 (TF32) / ' if tf32 else ''}{mma_per_product} MMAs per product",
+    }
+
+    # ---- end to end through host buffers (rank-local problem, max over ranks)
+    e2e = None
+    if args.e2e_steps > 0:
+        host = api.HostGemm(handle, device)
+        ah = torch.empty(a.numel(), dtype=torch.float32, pin_memory=True)
+        bh = torch.empty(b.numel(), dtype=torch.float32, pin_memory=True)
+        ch = torch.empty(c.numel(), dtype=torch.float32, pin_memory=True)
+        ah.copy_(a)
+        bh.copy_(b)
+        ch.copy_(c)
+        # the host path reuses the device-resident tensors as staging buffers
+        host._bufs = {"A": a, "B": b, "C": c}
+        torch.cuda.synchronize()
+        h2d, d2h = host.gemm(0, 0, m, n_local, k, 1.0, ah, m, bh, k, args.beta, ch, m, mode)
+        barrier()
+        e0.record()
+        for _ in range(args.e2e_steps):
+            h2d, d2h = host.gemm(0, 0, m, n_local, k, 1.0, ah, m, bh, k, args.beta, ch, m, mode)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        if dist is not None:
+            t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": 2.0 * m * (n_local * world) * k / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+               "steps": args.e2e_steps,
+               "note": "per rank: A, B, C copied from pinned host memory, C copied back; "
+                       "no NCCL broadcast on this leg"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tf, dt, cols = cpu_gemm_sample(n, 15.0)
+        cpu = {"value": tf, "unit": UNIT, "cores": host_cores(), "kind": "port",
+               "sample": f"FP32 host GEMM on {cols} of {n} columns of an m=k={n} problem "
+                         f"({dt:.1f} s, A packed inside the timed call)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16" if not tf32 else "tf32",
+            "data": "synthetic",
+            "config": {
+                "workload": (f"SGEMM {mode.name} NN column-major m=k={n}, n={n_local * world} "
+                             f"({n_local} columns per GPU), alpha=1, beta={args.beta}, "
+                             "A,B ~ U(-1,1)*2^e e in [-8,8], C ~ U(-1,1)"),
+                "parallelism": ("single GPU" if world == 1 else
+                                f"C/B column blocks over {world} GPUs, A broadcast from rank 0 "
+                                "with NCCL inside every step"),
+                "l2": "inputs (1 GiB per matrix) exceed the 126 MB L2; no explicit flush",
+            },
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": 3 * args.steps * (2 if mode == api.ComputeMode.AUTO else 1),
+            "kernel_status": kstatus, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    handle.destroy()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n", type=int, default=16384)
+    ap.add_argument("--mode", default="FP16TCEC")
+    ap.add_argument("--beta", type=float, default=0.5)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -197,6 +197,15 @@ class Handle:
     def set_workspace_limit(self, nbytes: int) -> None:
         self._lib.cuMpSGEMM_set_workspace_limit(self._h, nbytes)
 
+    def set_kernel_timing(self, enable: bool) -> None:
+        self._lib.cuMpSGEMM_set_kernel_timing(self._h, 1 if enable else 0)
+
+    def get_kernel_timing(self) -> Tuple[int, float, float]:
+        """(launch groups, summed split-pass ms, summed GEMM-kernel ms) since the last query."""
+        s, g = C.c_double(0), C.c_double(0)
+        n = self._lib.cuMpSGEMM_get_kernel_timing(self._h, C.byref(s), C.byref(g))
+        return int(n), s.value, g.value
+
     # ------------------------------------------------------------------ statistics
     def exp_stats_ext(self, m, n, ptr: DevPtr, ld, batch_size=1, stride=0,
                       complex: Optional[bool] = None) -> int:
@@ -362,3 +371,44 @@ def matmul(handle: Handle, A, B, mode: int = ComputeMode.FP16TCEC, out=None, alp
     handle.gemm_strided_batch(CUBLAS_OP_N, CUBLAS_OP_N, n, m, k, alpha, B, n, k * n, A, k, m * k,
                               beta, out, n, m * n, bsz, mode)
     return out
+
+
+class HostGemm:
+    """GEMM on operands that live in (pinned) host memory.
+
+    Each call copies A, B (and C when beta != 0) to the device on the handle's stream, runs
+    the GEMM and copies C back; device staging buffers are kept between calls.  This is the
+    path a caller takes whose matrices are not resident on the GPU, e.g. a host BLAS client.
+    """
+
+    def __init__(self, handle: Handle, device=None):
+        import torch
+
+        self.handle = handle
+        self.torch = torch
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self._bufs = {}
+
+    def _staging(self, key, host_tensor):
+        t = self._bufs.get(key)
+        if t is None or t.numel() != host_tensor.numel() or t.dtype != host_tensor.dtype:
+            t = self.torch.empty(host_tensor.numel(), dtype=host_tensor.dtype, device=self.device)
+            self._bufs[key] = t
+        return t
+
+    def gemm(self, op_A, op_B, m, n, k, alpha, A_host, lda, B_host, ldb, beta, C_host, ldc, mode):
+        """Returns (bytes copied host->device, bytes copied device->host)."""
+        dA = self._staging("A", A_host)
+        dB = self._staging("B", B_host)
+        dC = self._staging("C", C_host)
+        h2d = 0
+        dA.copy_(A_host.reshape(-1), non_blocking=True)
+        dB.copy_(B_host.reshape(-1), non_blocking=True)
+        h2d += A_host.numel() * A_host.element_size() + B_host.numel() * B_host.element_size()
+        if complex(beta) != 0:
+            dC.copy_(C_host.reshape(-1), non_blocking=True)
+            h2d += C_host.numel() * C_host.element_size()
+        self.handle.gemm(op_A, op_B, m, n, k, alpha, dA, lda, dB, ldb, beta, dC, ldc, mode)
+        C_host.reshape(-1).copy_(dC, non_blocking=True)
+        d2h = C_host.numel() * C_host.element_size()
+        return h2d, d2h

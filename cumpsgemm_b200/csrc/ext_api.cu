@@ -201,6 +201,32 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t h, size_t bytes) {
   h->workspace_limit_bytes = bytes;
 }
 
+void cuMpSGEMM_set_kernel_timing(cuMpSGEMM_handle_t h, int enable) {
+  h->kernel_timing = enable != 0;
+}
+
+unsigned long long cuMpSGEMM_get_kernel_timing(cuMpSGEMM_handle_t h, double *split_ms,
+                                               double *gemm_ms) {
+  DeviceGuard guard(h->device);
+  cudaStreamSynchronize(h->cuda_stream);
+  double s = 0, g = 0;
+  unsigned long long n = 0;
+  for (auto &tt : h->timing_events) {
+    float a = 0.f, b = 0.f;
+    if (cudaEventElapsedTime(&a, tt.e[0], tt.e[1]) == cudaSuccess &&
+        cudaEventElapsedTime(&b, tt.e[1], tt.e[2]) == cudaSuccess) {
+      s += a;
+      g += b;
+      ++n;
+    }
+    for (auto &e : tt.e) cudaEventDestroy(e);
+  }
+  h->timing_events.clear();
+  if (split_ms) *split_ms = s;
+  if (gemm_ms) *gemm_ms = g;
+  return n;
+}
+
 // ---- hijack control
 cuMpSGEMM_handle_t cuMpSGEMM_hijack_get_internal_global_handle(void) {
   return cumpsgemm::hijack_control::get_internal_global_handle();

@@ -175,6 +175,11 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       sa.k_pad = k_pad;
       sa.with_lo = ec;
       sa.dyn = dyn;
+      cuMpSGEMM_handle::TimingTriple tt{};
+      if (h->kernel_timing) {
+        for (auto &e : tt.e) cudaEventCreate(&e);
+        cudaEventRecord(tt.e[0], h->cuda_stream);
+      }
       err = launch_split(sa, h->cuda_stream);
       if (err != cudaSuccess) break;
       SplitArgs sb = sa;
@@ -189,6 +194,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       sb.rows_pad = rows_pad_b;
       err = launch_split(sb, h->cuda_stream);
       if (err != cudaSuccess) break;
+      if (h->kernel_timing) cudaEventRecord(tt.e[1], h->cuda_stream);
 
       TcecGemmArgs g;
       g.kind = kind;
@@ -213,6 +219,10 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       g.tile_n = tile_n;
       g.dev_status = h->dev_status;
       err = launch_tcec_gemm(g, h->cuda_stream);
+      if (h->kernel_timing) {
+        cudaEventRecord(tt.e[2], h->cuda_stream);
+        h->timing_events.push_back(tt);
+      }
     }
   }
   if (prof) h->exp_stats.profiler.stop("gemm_kernel", h->cuda_stream);

@@ -7,6 +7,7 @@
 #include <string>
 #include <unordered_map>
 #include <utility>
+#include <vector>
 
 #include <cuComplex.h>
 #include <cuda_runtime.h>
@@ -110,6 +111,14 @@ struct cuMpSGEMM_handle {
 
   // Device status word the GEMM kernel writes when a bounded wait gives up.
   int *dev_status = nullptr;
+
+  // Optional per-launch timing: events recorded on the launching stream before the split
+  // pass, between split pass and GEMM kernel, and after the GEMM kernel.
+  struct TimingTriple {
+    cudaEvent_t e[3];
+  };
+  bool kernel_timing = false;
+  std::vector<TimingTriple> timing_events;
 };
 
 namespace cumpsgemm_b200 {

@@ -1,0 +1,158 @@
+"""Multi-GPU partitioning of the TCEC GEMM path (one process per GPU).
+
+The reference is single-GPU (device 0 is hard-coded, ``src/handle.cu:12-21``);
+this module adds the two partitions the path admits without any collective in
+the inner loop:
+
+* strided-batch calls are split by contiguous batch ranges, every rank keeping
+  its own A_b, B_b, C_b;
+* a single large GEMM is split by column blocks of C: B and C blocks are
+  resident on their rank, A is broadcast once over NCCL into each rank's own
+  memory, after which every kernel reads local memory only.
+
+For ``AUTO`` and ``FP16TCEC_SCALING`` the reference's decision and scale factor
+cover the whole operand (``src/exp_stats.cu:81-82,163-165``), so the statistics
+slots are all-reduced between the stages (max of the exponent bits, sums of the
+two counters); every rank then takes the same decision as a 1-GPU run would.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+from .api import CUBLAS_OP_N, ComputeMode, Handle
+
+
+def batch_range(batch_count: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [begin, end) of the batches owned by `rank`; sizes differ by at most one."""
+    if world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError("bad rank / world size")
+    base, extra = divmod(batch_count, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def column_range(n: int, world_size: int, rank: int, align: int = 1) -> Tuple[int, int]:
+    """Contiguous [begin, end) of the columns of C (and of op(B)) owned by `rank`.
+
+    Block boundaries are multiples of `align` (except the end of the matrix)."""
+    if world_size <= 0 or not (0 <= rank < world_size) or align <= 0:
+        raise ValueError("bad rank / world size / alignment")
+    blocks = (n + align - 1) // align
+    b0, b1 = batch_range(blocks, world_size, rank)
+    return min(b0 * align, n), min(b1 * align, n)
+
+
+class ShardedGemm:
+    """Runs one rank's share of a partitioned GEMM.  `group` is a torch.distributed group
+    (None = default group); with a world size of 1 no collective is issued."""
+
+    def __init__(self, handle: Handle, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.handle = handle
+        self.group = group
+        self.dist = dist
+        self.torch = torch
+        self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._words = None
+
+    # ------------------------------------------------------------------ statistics
+    def _global_rank(self, group_rank: int) -> int:
+        if self.group is None:
+            return group_rank
+        return self.dist.get_global_rank(self.group, group_rank)
+
+    def _allreduce_slot(self, stats_id: int, device) -> None:
+        """max over ranks of word 0 (exponent bits), sum over ranks of words 1..2 (counters)."""
+        if self.world_size == 1:
+            return
+        torch, dist = self.torch, self.dist
+        if self._words is None or self._words.device != device:
+            self._words = torch.zeros(4, dtype=torch.int64, device=device)
+        w = self._words
+        self.handle.exp_stats_export(stats_id, w)
+        dist.all_reduce(w[0:1], op=dist.ReduceOp.MAX, group=self.group)
+        dist.all_reduce(w[1:3], op=dist.ReduceOp.SUM, group=self.group)
+        self.handle.exp_stats_import(stats_id, w)
+
+    def global_exp_stats(self, m, n, ptr, ld, batch_size=1, stride=0, replicated=False) -> int:
+        """Statistics slot whose content equals what one GPU holding the whole operand would
+        compute.  `replicated`: every rank holds the same full operand (no reduction needed)."""
+        h = self.handle
+        sid = h.exp_stats_begin()
+        h.exp_stats_stage(1, sid, m, n, ptr, ld, batch_size, stride)
+        if not replicated:
+            self._allreduce_slot(sid, ptr.device)
+        h.exp_stats_decide(1, sid)
+        if replicated or self.world_size == 1:
+            h.exp_stats_stage(2, sid, m, n, ptr, ld, batch_size, stride)
+        else:
+            # After decision 1 the counters are either zero (undecided: stage 2 recounts) or
+            # already global (decided: stage 2 is skipped on the device).  Only what stage 2
+            # adds locally may be summed over the ranks.
+            torch, dist = self.torch, self.dist
+            w = self._words
+            h.exp_stats_export(sid, w)
+            base = w.clone()
+            h.exp_stats_stage(2, sid, m, n, ptr, ld, batch_size, stride)
+            h.exp_stats_export(sid, w)
+            delta = w[1:3] - base[1:3]
+            dist.all_reduce(delta, op=dist.ReduceOp.SUM, group=self.group)
+            w[1:3] = base[1:3] + delta
+            h.exp_stats_import(sid, w)
+        h.exp_stats_decide(2, sid)
+        return sid
+
+    def global_exp_max(self, m, n, ptr, ld, batch_size=1, stride=0, replicated=False) -> int:
+        h = self.handle
+        sid = h.exp_stats_begin()
+        h.exp_stats_stage(3, sid, m, n, ptr, ld, batch_size, stride)
+        if not replicated:
+            self._allreduce_slot(sid, ptr.device)
+        return sid
+
+    def _stats_for(self, mode, op, rows, cols, ptr, ld, batch, stride, replicated):
+        sm, sn = (rows, cols) if op == CUBLAS_OP_N else (cols, rows)
+        stride_arg = stride if batch > 1 else 0
+        if mode == ComputeMode.AUTO:
+            return self.global_exp_stats(sm, sn, ptr, ld, batch, stride_arg, replicated)
+        return self.global_exp_max(sm, sn, ptr, ld, batch, stride_arg, replicated)
+
+    # ------------------------------------------------------------------ batch partition
+    def gemm_strided_batch_local(self, op_A, op_B, m, n, k, alpha, A, lda, stridea, B, ldb,
+                                 strideb, beta, Cmat, ldc, stridec, local_batch_count, mode):
+        """This rank's batches of a strided-batch GEMM whose batches are spread over the ranks.
+        A, B, Cmat hold only the local batches."""
+        mode = ComputeMode(mode)
+        h = self.handle
+        if mode in (ComputeMode.AUTO, ComputeMode.FP16TCEC_SCALING):
+            ida = self._stats_for(mode, op_A, m, k, A, lda, local_batch_count, stridea, False)
+            idb = self._stats_for(mode, op_B, k, n, B, ldb, local_batch_count, strideb, False)
+            return h.gemm_strided_batch_with_stats(op_A, op_B, m, n, k, alpha, A, lda, stridea, B,
+                                                   ldb, strideb, beta, Cmat, ldc, stridec,
+                                                   local_batch_count, mode, ida, idb)
+        return h.gemm_strided_batch(op_A, op_B, m, n, k, alpha, A, lda, stridea, B, ldb, strideb,
+                                    beta, Cmat, ldc, stridec, local_batch_count, mode)
+
+    # ------------------------------------------------------------------ column partition
+    def gemm_column_block(self, op_A, op_B, m, n_local, k, alpha, A, lda, B_local, ldb, beta,
+                          C_local, ldc, mode, root: int = 0, broadcast_A: bool = True):
+        """This rank's column block C[:, J] = alpha*op(A)*op(B)[:, J] + beta*C[:, J].
+
+        A must be a tensor of the full stored extent on every rank; its content is taken from
+        `root` (one NCCL broadcast into local memory) unless broadcast_A is False, in which
+        case every rank already holds it."""
+        mode = ComputeMode(mode)
+        h = self.handle
+        if broadcast_A and self.world_size > 1:
+            self.dist.broadcast(A, src=self._global_rank(root), group=self.group)
+        if mode in (ComputeMode.AUTO, ComputeMode.FP16TCEC_SCALING):
+            ida = self._stats_for(mode, op_A, m, k, A, lda, 1, 0, True)
+            idb = self._stats_for(mode, op_B, k, n_local, B_local, ldb, 1, 0, False)
+            return h.gemm_strided_batch_with_stats(op_A, op_B, m, n_local, k, alpha, A, lda, 0,
+                                                   B_local, ldb, 0, beta, C_local, ldc, 0, 1,
+                                                   mode, ida, idb)
+        return h.gemm(op_A, op_B, m, n_local, k, alpha, A, lda, B_local, ldb, beta, C_local, ldc,
+                      mode)

@@ -128,6 +128,14 @@ int cuMpSGEMM_get_kernel_status(cuMpSGEMM_handle_t handle);
 /* Cap (bytes) for the operand workspace a strided-batch call may use at once; batches beyond
  * it are processed in chunks.  0 restores the default (8 GiB). */
 void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
+/* Per-launch device timing with CUDA events on the handle's stream (off by default).  While
+ * enabled every split + GEMM launch group records three events; get_kernel_timing
+ * synchronises the stream, returns the number of launch groups since the last query and the
+ * summed durations of the split passes and of the GEMM kernels, and clears the record.
+ * In AUTO mode both gated kinds are recorded, the deselected one with near-zero time. */
+void cuMpSGEMM_set_kernel_timing(cuMpSGEMM_handle_t handle, int enable);
+unsigned long long cuMpSGEMM_get_kernel_timing(cuMpSGEMM_handle_t handle, double *split_ms,
+                                               double *gemm_ms);
 
 /* ---- interception-layer control (cumpsgemm::hijack_control, reference:
  *      src/cumpsgemm_cublas.cu:1189-1271) ---------------------------------- */

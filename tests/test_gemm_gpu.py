@@ -1,0 +1,275 @@
+"""Parity of the CUDA GEMM path (through the C ABI) with the FP64 oracle.
+
+Pass criterion for the error-corrected modes is the reference's own:
+relative Frobenius residual against FP64 below 2^-23 * sqrt(K)
+(test/main.cu:68-74, 372-375); the non-corrected modes use 2^-10 * sqrt(K).
+On top of it the benchmark's stated bar is checked: mean relative error at most
+1e-6 for well-scaled inputs and errors no worse than an FP32 GEMM's.
+"""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+N, T, Cj = 0, 1, 2
+FP16TCEC, TF32TCEC, FP16TC, TF32TC, DRY_RUN, AUTO, SCALING = 1, 2, 3, 4, 8, 9, 11
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _dev(x):
+    return _torch().from_numpy(x).cuda()
+
+
+def _run_real(handle, oracle, op_a, op_b, m, n, k, mode, alpha=1.0, beta=0.0, pad=(0, 0, 0),
+              seed=0, gen=None):
+    gen = gen or oracle.gen_uniform
+    am, an = (m, k) if op_a == N else (k, m)
+    bm, bn = (k, n) if op_b == N else (n, k)
+    lda, ldb, ldc = am + pad[0], bm + pad[1], m + pad[2]
+    a = gen(seed, lda * an)
+    b = gen(seed + 1, ldb * bn)
+    c0 = oracle.gen_uniform(seed + 2, ldc * n)
+    da, db, dc = _dev(a), _dev(b), _dev(c0.copy())
+    handle.gemm(op_a, op_b, m, n, k, alpha, da, lda, db, ldb, beta, dc, ldc, mode)
+    res = dc.cpu().numpy()
+    truth = oracle.gemm_f64(op_a, op_b, m, n, k, alpha, a, lda, b, ldb, beta, c0, ldc)
+    return a, b, c0, res, truth, (lda, ldb, ldc)
+
+
+def test_config1_sgemm_1024_fp16tcec(handle, oracle):
+    """Benchmark config 1: m=n=k=1024, NN, alpha=1, beta=0, uniform(-1,1), seed 0."""
+    m = n = k = 1024
+    a, b, c0, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, FP16TCEC, seed=0)
+    r = oracle.residual(truth, res, m)
+    assert r < oracle.error_threshold(True, k)
+    c32 = np.zeros(m * n, dtype=np.float32)
+    oracle.gemm_f32(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c32, m)
+    mx, mean = oracle.relative_errors(truth, res, m)
+    mx32, mean32 = oracle.relative_errors(truth, c32, m)
+    assert mean <= 1e-6
+    assert mean <= 1.5 * mean32          # no worse than FP32 SIMT on the same inputs
+    assert r <= 1.5 * oracle.residual(truth, c32, m)
+
+
+def test_reference_input_distribution_normal(handle, oracle):
+    """The reference's own test inputs: N(0,1) (test/main.cu:552-558)."""
+    m = n = k = 512
+    for mode in (FP16TCEC, TF32TCEC):
+        _, _, _, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, mode, seed=3,
+                                           gen=oracle.gen_normal)
+        assert oracle.residual(truth, res, m) < oracle.error_threshold(True, k)
+
+
+@pytest.mark.parametrize("mode", [FP16TCEC, TF32TCEC])
+def test_config2_row_2048(handle, oracle, mode):
+    """Benchmark config 2 at N=2048: inputs u*2^e, e in [-8,8]; alpha=1, beta=0.5."""
+    m = n = k = 2048
+    a, b, c0, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, mode, beta=0.5, seed=1,
+                                        gen=oracle.gen_uniform_exp)
+    r = oracle.residual(truth, res, m)
+    assert r < oracle.error_threshold(True, k)
+    c32 = c0.copy()
+    oracle.gemm_f32(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c32, m)
+    assert r <= 1.5 * oracle.residual(truth, c32, m)
+
+
+@pytest.mark.parametrize("op_a", [N, T])
+@pytest.mark.parametrize("op_b", [N, T])
+@pytest.mark.parametrize("mode", [FP16TCEC, TF32TCEC])
+def test_sgemm_ops_and_ragged_shapes(handle, oracle, op_a, op_b, mode):
+    for (m, n, k, pad) in [(200, 300, 100, (0, 0, 0)), (129, 257, 65, (3, 5, 7)), (64, 64, 64, (1, 1, 1))]:
+        _, _, _, res, truth, ld = _run_real(handle, oracle, op_a, op_b, m, n, k, mode, alpha=-1.25,
+                                            beta=0.75, pad=pad, seed=m + n)
+        assert oracle.residual(truth, res[: ld[2] * n].reshape(-1), ld[2]) < \
+            oracle.error_threshold(True, k)
+        # rows between m and ldc must be untouched
+        if pad[2]:
+            c0 = oracle.gen_uniform(m + n + 2, ld[2] * n).reshape((ld[2], n), order="F")
+            got = res.reshape((ld[2], n), order="F")
+            np.testing.assert_array_equal(got[m:], c0[m:])
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (1, 513, 7), (300, 1, 33), (5, 3, 1), (127, 63, 4097)])
+def test_sgemm_degenerate_shapes(handle, oracle, shape):
+    m, n, k = shape
+    _, _, _, res, truth, _ = _run_real(handle, oracle, N, T, m, n, k, FP16TCEC, beta=1.0, seed=11)
+    assert oracle.residual(truth, res, m) < oracle.error_threshold(True, max(k, 16))
+
+
+@pytest.mark.parametrize("tile", [64, 128, 256])
+def test_every_tile_width(handle, oracle, tile):
+    os.environ["CUMPSGEMM_TILE_N"] = str(tile)
+    try:
+        m, n, k = 384, 520, 200
+        _, _, _, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, FP16TCEC, beta=0.5, seed=5)
+        assert oracle.residual(truth, res, m) < oracle.error_threshold(True, k)
+        _, _, _, res, truth, _ = _run_real(handle, oracle, T, N, m, n, k, TF32TCEC, seed=6)
+        assert oracle.residual(truth, res, m) < oracle.error_threshold(True, k)
+    finally:
+        os.environ.pop("CUMPSGEMM_TILE_N", None)
+
+
+def test_tile_choice_is_reported(handle, oracle):
+    torch = _torch()
+    big = torch.zeros(4096 * 4096, device="cuda")
+    st, mod = handle.gemm_module(N, N, 4096, 4096, 64, 1.0, big, 4096, big, 64, 0.0, big, 4096,
+                                 FP16TCEC)
+    assert st == 0 and mod == 0          # 128x256 tiles fill the GPU
+    st, mod = handle.gemm_module(N, N, 128, 128, 64, 1.0, big, 128, big, 64, 0.0, big, 128, FP16TCEC)
+    assert st == 0 and mod == 2          # a single small problem takes the narrow tile
+
+
+def _run_complex(handle, oracle, op_a, op_b, m, n, k, mode, alpha, beta, seed=0, pad=0):
+    am, an = (m, k) if op_a == N else (k, m)
+    bm, bn = (k, n) if op_b == N else (n, k)
+    lda, ldb, ldc = am + pad, bm + pad, m + pad
+
+    def cgen(s, count):
+        return (oracle.gen_uniform(s, count) + 1j * oracle.gen_uniform(s + 100, count)).astype(np.complex64)
+
+    a, b, c0 = cgen(seed, lda * an), cgen(seed + 1, ldb * bn), cgen(seed + 2, ldc * n)
+    da, db, dc = _dev(a), _dev(b), _dev(c0.copy())
+    handle.gemm(op_a, op_b, m, n, k, alpha, da, lda, db, ldb, beta, dc, ldc, mode)
+    truth = oracle.gemm_f64(op_a, op_b, m, n, k, alpha, a, lda, b, ldb, beta, c0, ldc)
+    return oracle.residual(truth, dc.cpu().numpy(), ldc)
+
+
+@pytest.mark.parametrize("op_a", [N, T, Cj])
+@pytest.mark.parametrize("op_b", [N, T, Cj])
+def test_cgemm_all_op_pairs(handle, oracle, op_a, op_b):
+    """The reference tests {N,T,C}^2 for complex (test/main.cu:539-629)."""
+    for mode in (FP16TCEC, TF32TCEC):
+        r = _run_complex(handle, oracle, op_a, op_b, 70, 90, 50, mode, 1.0, 0.0, seed=op_a * 3 + op_b)
+        assert r < oracle.error_threshold(True, 50)
+    r = _run_complex(handle, oracle, op_a, op_b, 33, 65, 129, FP16TCEC, 0.5 - 1.5j, -0.25 + 2j,
+                     seed=9, pad=3)
+    assert r < oracle.error_threshold(True, 129)
+
+
+def test_cgemm_square_256(handle, oracle):
+    """Per-batch shape of benchmark config 4 (complex 256^3)."""
+    r = _run_complex(handle, oracle, N, N, 256, 256, 256, FP16TCEC, 1.0, 0.0, seed=21)
+    assert r < oracle.error_threshold(True, 256)
+
+
+@pytest.mark.parametrize("mode", [FP16TC, TF32TC])
+def test_uncorrected_modes(handle, oracle, mode):
+    m = n = k = 256
+    _, _, _, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, mode, seed=2)
+    r = oracle.residual(truth, res, m)
+    assert r < oracle.error_threshold(False, k)
+    assert r > 1e-6                      # really is the uncorrected arithmetic
+
+
+def test_strided_batch_sgemm_and_cgemm(handle, oracle):
+    torch = _torch()
+    batch, m, n, k = 5, 96, 130, 70
+    sa, sb, sc = m * k + 8, k * n + 4, m * n
+    a = oracle.gen_uniform(1, sa * batch)
+    b = oracle.gen_uniform(2, sb * batch)
+    c0 = oracle.gen_uniform(3, sc * batch)
+    da, db, dc = _dev(a), _dev(b), _dev(c0.copy())
+    handle.gemm_strided_batch(N, N, m, n, k, 2.0, da, m, sa, db, k, sb, 0.5, dc, m, sc, batch,
+                              FP16TCEC)
+    res = dc.cpu().numpy()
+    for i in range(batch):
+        truth = oracle.gemm_f64(N, N, m, n, k, 2.0, a[i * sa:], m, b[i * sb:], k, 0.5, c0[i * sc:], m)
+        assert oracle.residual(truth, res[i * sc:(i + 1) * sc], m) < oracle.error_threshold(True, k)
+    # chunked workspace: same numbers when the batch is processed in pieces
+    handle.set_workspace_limit(1 << 20)
+    dc2 = _dev(c0.copy())
+    handle.gemm_strided_batch(N, N, m, n, k, 2.0, da, m, sa, db, k, sb, 0.5, dc2, m, sc, batch,
+                              FP16TCEC)
+    handle.set_workspace_limit(0)
+    assert torch.equal(dc, dc2)
+    # complex batch, stride 0 on B (one matrix shared by every batch)
+    za = (oracle.gen_uniform(4, m * k * batch) + 1j * oracle.gen_uniform(5, m * k * batch)).astype(np.complex64)
+    zb = (oracle.gen_uniform(6, k * n) + 1j * oracle.gen_uniform(7, k * n)).astype(np.complex64)
+    dza, dzb = _dev(za), _dev(zb)
+    dzc = torch.zeros(m * n * batch, dtype=torch.complex64, device="cuda")
+    handle.gemm_strided_batch(N, N, m, n, k, 1.0, dza, m, m * k, dzb, k, 0, 0.0, dzc, m, m * n,
+                              batch, TF32TCEC)
+    zres = dzc.cpu().numpy()
+    for i in range(batch):
+        truth = oracle.gemm_f64(N, N, m, n, k, 1.0, za[i * m * k:], m, zb, k, 0.0, None, m)
+        assert oracle.residual(truth, zres[i * m * n:(i + 1) * m * n], m) < oracle.error_threshold(True, k)
+
+
+def test_beta_zero_ignores_nan_in_c(handle, oracle):
+    torch = _torch()
+    m = n = k = 128
+    a, b = _dev(oracle.gen_uniform(1, m * k)), _dev(oracle.gen_uniform(2, k * n))
+    c = torch.full((m * n,), float("nan"), device="cuda")
+    handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, FP16TCEC)
+    assert torch.isfinite(c).all()
+
+
+def test_dry_run_and_argument_errors(handle, oracle):
+    from cumpsgemm_b200 import api
+
+    torch = _torch()
+    m = n = k = 64
+    a = torch.ones(m * k, device="cuda")
+    c = torch.full((m * n,), 7.0, device="cuda")
+    assert handle.gemm(N, N, m, n, k, 1.0, a, m, a, k, 0.0, c, m, DRY_RUN) == 0
+    assert (c == 7.0).all()
+    inv = api.CUBLAS_STATUS_INVALID_VALUE
+    assert handle.gemm(N, N, 0, n, k, 1.0, a, m, a, k, 0.0, c, m, FP16TCEC, check=False) == inv
+    assert handle.gemm(N, N, m, n, k, 1.0, a, m - 1, a, k, 0.0, c, m, FP16TCEC, check=False) == inv
+    assert handle.gemm(Cj, N, m, n, k, 1.0, a, m, a, k, 0.0, c, m, FP16TCEC, check=False) == inv
+    assert handle.gemm(N, N, m, n, k, 1.0, a, m, a, k, 0.0, c, m, 0, check=False) == \
+        api.CUBLAS_STATUS_NOT_SUPPORTED
+    assert (c == 7.0).all()
+
+
+def test_power_of_two_scaling_commutes_bitwise(handle, oracle):
+    """Size-independent property: scaling A by 2^p scales C by 2^p exactly (no overflow)."""
+    torch = _torch()
+    m = n = k = 1024
+    a = _dev(oracle.gen_uniform_exp(1, m * k))
+    b = _dev(oracle.gen_uniform_exp(2, k * n))
+    c1 = torch.zeros(m * n, device="cuda")
+    c2 = torch.zeros(m * n, device="cuda")
+    for mode in (FP16TCEC, TF32TCEC):
+        handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c1, m, mode)
+        handle.gemm(N, N, m, n, k, 1.0, a * 4.0, m, b * 0.5, k, 0.0, c2, m, mode)
+        assert torch.equal(c1 * 2.0, c2)
+        handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c2, m, mode)   # run-to-run determinism
+        assert torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("n", [8192])
+def test_large_size_against_sampled_fp64(handle, oracle, n):
+    """Full-size check: FP64 truth on sampled rows of C (CPU oracle) plus bitwise properties."""
+    torch = _torch()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    a = torch.rand(n * n, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(n * n, device="cuda", generator=g) * 2 - 1
+    c0 = torch.rand(n * n, device="cuda", generator=g) * 2 - 1
+    c = c0.clone()
+    handle.gemm(N, N, n, n, n, 1.0, a, n, b, n, 0.5, c, n, FP16TCEC)
+    ah, bh, c0h, ch = (x.cpu().numpy() for x in (a, b, c0, c))
+    rows = [0, 1, 127, 128, n // 2 + 3, n - 1]
+    for i in rows:
+        # row i of C: op(A) restricted to one row = pointer offset i with the same lda
+        truth = oracle.gemm_f64(N, N, 1, n, n, 1.0, ah[i:], n, bh, n, 0.5, c0h[i:], n)
+        got = ch.reshape((n, n), order="F")[i].copy()
+        assert oracle.residual(truth, got, 1) < oracle.error_threshold(True, n)
+    cols = [0, 255, 256, n - 1]
+    for j in cols:
+        truth = oracle.gemm_f64(N, N, n, 1, n, 1.0, ah, n, bh[j * n:], n, 0.5, c0h[j * n:], n)
+        assert oracle.residual(truth, ch[j * n:(j + 1) * n], n) < oracle.error_threshold(True, n)
+    # whole-matrix cross-check against the GPU's own FP64 GEMM
+    A = a.view(n, n).t().double()
+    B = b.view(n, n).t().double()
+    truth_gpu = (A @ B + 0.5 * c0.view(n, n).t().double())
+    diff = (truth_gpu - c.view(n, n).t().double()).norm() / truth_gpu.norm()
+    assert diff.item() < oracle.error_threshold(True, n)
