@@ -109,6 +109,7 @@ PROTOTYPES = {
     "cuMpSGEMM_exp_stats_import": (None, [vp, u32, vp]),
     "cuMpSGEMM_sgemm_strided_batch_with_stats": (i32, _GEMM_SB_ARGS + [u32, u32]),
     "cuMpSGEMM_cgemm_strided_batch_with_stats": (i32, _GEMM_SB_ARGS + [u32, u32]),
+    "cuMpSGEMM_sgemm_static_scratch": (i32, [vp] + _GEMM_ARGS[1:]),
     # intercepted cuBLAS symbols (prototypes of cublas_api.h)
     "cublasSgemm_v2": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32]),
     "cublasCgemm_v2": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32]),

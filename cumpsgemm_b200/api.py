@@ -346,6 +346,24 @@ class Handle:
         return (t.value, n.value) if ok else None
 
 
+def sgemm_static_scratch(stream, op_A: int, op_B: int, m: int, n: int, k: int, alpha, A: DevPtr,
+                         lda: int, B: DevPtr, ldb: int, beta, Cmat: DevPtr, ldc: int,
+                         mode: int) -> int:
+    """cuMpSGEMM_sgemm_static_scratch: handle-free FP32 GEMM that allocates nothing.
+
+    For callers that must not call cudaMalloc: the split operand panels go to a 32 MiB array
+    built into the library (problems that need more are rejected with INVALID_VALUE).  Calls
+    that overlap in time on one GPU race on that array; make the first call on a device
+    outside any stream capture.  `stream` is a torch stream, a raw cudaStream_t or None.
+    Returns the cublasStatus_t."""
+    lib = _lib.load()
+    s = 0 if stream is None else getattr(stream, "cuda_stream", stream)
+    a, b = _scalar(alpha, False), _scalar(beta, False)
+    return lib.cuMpSGEMM_sgemm_static_scratch(C.c_void_p(int(s)), op_A, op_B, m, n, k,
+                                              C.cast(a, C.c_void_p), _ptr(A), lda, _ptr(B), ldb,
+                                              C.cast(b, C.c_void_p), _ptr(Cmat), ldc, int(mode))
+
+
 # ---------------------------------------------------------------------- convenience
 def matmul(handle: Handle, A, B, mode: int = ComputeMode.FP16TCEC, out=None, alpha=1.0, beta=0.0):
     """Row-major ``A @ B`` for contiguous 2-D (or batched 3-D) torch CUDA tensors.

@@ -34,6 +34,7 @@ CUDA_SOURCES = [
     "tcec_gemm.cu",
     "gemm_api.cu",
     "ext_api.cu",
+    "static_scratch_gemm.cu",
 ]
 CPP_SOURCES = ["cublas_shim.cpp", "default_rule.cpp"]
 

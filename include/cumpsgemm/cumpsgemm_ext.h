@@ -202,6 +202,27 @@ cublasStatus_t cuMpSGEMM_cgemm_strided_batch_with_stats(
     cuComplex *c, uint64_t ldc, uint64_t stridec, uint64_t batch_count,
     cuMpSGEMM_compute_mode_t mode, unsigned stats_id_a, unsigned stats_id_b);
 
+/* ---- allocation-free FP32 GEMM ------------------------------------------- */
+/* No counterpart in the reference.  For callers that may not allocate device memory (a
+ * process whose memory budget is fixed at start-up, a loop that cannot take the device
+ * synchronisation cudaMalloc / cudaFree imply, code without a handle): same arithmetic as
+ * cuMpSGEMM_sgemm in FP16TCEC or TF32TCEC mode, but the split operand panels live in a 32 MiB
+ * array built into the library instead of a workspace obtained with cudaMalloc, and no handle
+ * is needed.  The call issues kernel launches on `stream` and nothing else.
+ *   - Problems whose panels exceed 32 MiB (FP16TCEC: 4*(round_up(m,128)+round_up(n,tile))*
+ *     round_up(k,64) bytes, twice that for TF32TCEC; m=n=k=2048 FP16TCEC just fits) return
+ *     CUBLAS_STATUS_INVALID_VALUE with an error line and launch nothing.
+ *   - The first call on a device resolves the array's device address and configures the
+ *     kernels; issue it before any stream capture on that device.
+ *   - The array is shared by all calls on a GPU: calls that overlap in time on one GPU race.
+ *     Each call rewrites all of the region it reads, so no clearing is needed between calls.
+ *   - alpha / beta are host pointers; op C is rejected; no status word is kept (waits inside
+ *     the kernel remain bounded). */
+cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
+    cudaStream_t stream, cublasOperation_t op_A, cublasOperation_t op_B, uint64_t m, uint64_t n,
+    uint64_t k, const float *alpha, const float *a, uint64_t lda, const float *b, uint64_t ldb,
+    const float *beta, float *c, uint64_t ldc, cuMpSGEMM_compute_mode_t compute_mode);
+
 #ifdef __cplusplus
 }
 #endif
