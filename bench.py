@@ -292,7 +292,7 @@ def run_ours(args, rank, local_rank, world):
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak if peak else None, "traffic": None,
-        "kernel": "tcec_gemm_kernel (tcgen05, 128x256 tile)",
+        "kernel": "tcec_gemm_pair_kernel (tcgen05 cta_group::2, 256x256 tile per CTA pair)",
         "kernel_ms": gemm_ms_avg, "split_pass_ms": split_ms / max(groups, 1),
         "peak_source": f"{peaks['source']} dense 16-bit tensor peak "
                        f"({'sustained' if long_run else 'burst'}) {peak_dense} TFLOP/s / "

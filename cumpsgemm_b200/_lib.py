@@ -86,6 +86,7 @@ PROTOTYPES = {
     "cuMpSGEMM_sgemm_module": (i32, _GEMM_ARGS + [C.POINTER(u32)]),
     "cuMpSGEMM_get_kernel_status": (i32, [vp]),
     "cuMpSGEMM_set_workspace_limit": (None, [vp, C.c_size_t]),
+    "cuMpSGEMM_set_debug_buffer": (None, [vp, vp]),
     "cuMpSGEMM_set_kernel_timing": (None, [vp, i32]),
     "cuMpSGEMM_get_kernel_timing": (C.c_ulonglong, [vp, C.POINTER(C.c_double),
                                                     C.POINTER(C.c_double)]),

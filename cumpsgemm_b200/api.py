@@ -197,6 +197,10 @@ class Handle:
     def set_workspace_limit(self, nbytes: int) -> None:
         self._lib.cuMpSGEMM_set_workspace_limit(self._h, nbytes)
 
+    def set_debug_buffer(self, dev_words8) -> None:
+        """Stall-breakdown buffer (8 x int64 CUDA tensor) or None."""
+        self._lib.cuMpSGEMM_set_debug_buffer(self._h, 0 if dev_words8 is None else _ptr(dev_words8))
+
     def set_kernel_timing(self, enable: bool) -> None:
         self._lib.cuMpSGEMM_set_kernel_timing(self._h, 1 if enable else 0)
 

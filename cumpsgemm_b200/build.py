@@ -32,6 +32,7 @@ CUDA_SOURCES = [
     "dynamic_scaling.cu",
     "split_kernels.cu",
     "tcec_gemm.cu",
+    "tcec_gemm_pair.cu",
     "gemm_api.cu",
     "ext_api.cu",
     "static_scratch_gemm.cu",

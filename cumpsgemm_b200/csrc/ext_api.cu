@@ -201,6 +201,10 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t h, size_t bytes) {
   h->workspace_limit_bytes = bytes;
 }
 
+void cuMpSGEMM_set_debug_buffer(cuMpSGEMM_handle_t h, unsigned long long *dev_words8) {
+  h->debug_buffer = dev_words8;
+}
+
 void cuMpSGEMM_set_kernel_timing(cuMpSGEMM_handle_t h, int enable) {
   h->kernel_timing = enable != 0;
 }

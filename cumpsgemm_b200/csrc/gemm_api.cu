@@ -9,7 +9,7 @@
 // stream.  The reference's module table (364 instantiations per arch,
 // src/instance_sm80.cu) collapses to three tile widths because op N/T/C,
 // leading dimensions and edges are absorbed by the split pass.
-#include "internal.hpp"
+#include "gemm_common.cuh"
 
 #include <algorithm>
 #include <type_traits>
@@ -131,7 +131,12 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   if (used_kernel_module_id != nullptr)
     *used_kernel_module_id = (tile_n == 256) ? 0u : (tile_n == 128 ? 1u : 2u);
 
-  const std::uint32_t rows_pad_a = static_cast<std::uint32_t>(round_up(m_exp, 128));
+  // 256 x 256 tiles on CTA pairs whenever the wide tile is chosen for an error-corrected
+  // mode (CUMPSGEMM_PAIR=0 forces the single-CTA kernel).
+  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
+  const bool use_pair = ec && tile_n == 256 && !(pair_env != nullptr && pair_env[0] == '0');
+  const std::uint32_t rows_pad_a =
+      static_cast<std::uint32_t>(round_up(m_exp, use_pair ? 256 : 128));
   const std::uint32_t rows_pad_b = static_cast<std::uint32_t>(round_up(n, tile_n));
   const std::uint32_t k_pad = static_cast<std::uint32_t>(round_up(k_exp, 64));
   const std::size_t es_max = want_tf32 ? 4 : 2;
@@ -218,7 +223,9 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       g.dyn = dyn;
       g.tile_n = tile_n;
       g.dev_status = h->dev_status;
-      err = launch_tcec_gemm(g, h->cuda_stream);
+      g.debug = h->debug_buffer;
+      err = use_pair ? launch_tcec_gemm_pair(g, h->cuda_stream)
+                     : launch_tcec_gemm(g, h->cuda_stream);
       if (h->kernel_timing) {
         cudaEventRecord(tt.e[2], h->cuda_stream);
         h->timing_events.push_back(tt);

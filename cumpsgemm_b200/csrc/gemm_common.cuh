@@ -1,0 +1,38 @@
+// Pieces shared by the single-CTA and the CTA-pair TCEC GEMM kernels.
+#pragma once
+#include "internal.hpp"
+
+#include <cuda.h>
+
+namespace cumpsgemm_b200 {
+
+constexpr int kGemmRowBytes = 128; // K extent of one stage in bytes = one 128-byte swizzle atom
+
+// Kernel arguments besides the two tensor maps.
+struct GemmKernelParams {
+  float *c;
+  uint64_t ldc;
+  uint64_t stride_c;
+  uint32_t m, n;
+  uint32_t k_blocks;
+  uint32_t tiles_m, tiles_n;
+  float alpha_r, alpha_i, beta_r, beta_i;
+  float lo_scale_inv;
+  int is_complex;
+  const DynParams *dyn;
+  int *status;
+  // Optional stall breakdown (8 x u64, nullable): cycles the MMA issuer waited for operands [0]
+  // and for the accumulator drain [1], the producer for a free stage [2], drain warp 4 for
+  // a finished chunk [3]; MMA loop cycles [4]; contributing CTAs [5].
+  unsigned long long *debug;
+};
+
+// Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {128 bytes of K, box_rows, 1},
+// 128-byte swizzle.  Returns false if the driver entry point is unavailable or rejects it.
+bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_t k_pad,
+                    uint32_t rows_pad, uint32_t planes, uint32_t box_rows);
+
+// CTA-pair kernel (tcec_gemm_pair.cu): 256 x 256 tile per cluster of two CTAs.
+cudaError_t launch_tcec_gemm_pair(const TcecGemmArgs &a, cudaStream_t stream);
+
+} // namespace cumpsgemm_b200

@@ -118,6 +118,7 @@ struct cuMpSGEMM_handle {
     cudaEvent_t e[3];
   };
   bool kernel_timing = false;
+  unsigned long long *debug_buffer = nullptr; // caller-owned, see cuMpSGEMM_set_debug_buffer
   std::vector<TimingTriple> timing_events;
 };
 
@@ -181,6 +182,7 @@ struct TcecGemmArgs {
   const DynParams *dyn; // nullable
   int tile_n;           // 256, 128 or 64
   int *dev_status;
+  unsigned long long *debug = nullptr; // optional stall breakdown buffer (8 x u64)
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
 // Dynamic shared memory and stage count of a tile configuration (for tests/docs).

@@ -19,7 +19,7 @@
 // While the tensor core runs the two correction products of a stage the
 // epilogue warps drain D0 of the same stage, so D0 needs no double buffering
 // and the two accumulators fill the 512 TMEM columns at BN = 256.
-#include "internal.hpp"
+#include "gemm_common.cuh"
 #include "ptx.cuh"
 
 #include <mutex>
@@ -28,7 +28,7 @@ namespace cumpsgemm_b200 {
 namespace {
 
 constexpr int BM = 128;
-constexpr int ROW_BYTES = 128; // K extent of one stage in bytes = one 128-byte swizzle atom
+constexpr int ROW_BYTES = kGemmRowBytes;
 constexpr int NUM_THREADS = 384;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
@@ -45,19 +45,7 @@ template <int BN, bool EC> struct TileCfg {
   static_assert(STAGES >= 2, "need at least two stages");
 };
 
-struct KernelParams {
-  float *c;
-  uint64_t ldc;
-  uint64_t stride_c;
-  uint32_t m, n;
-  uint32_t k_blocks;
-  uint32_t tiles_m, tiles_n;
-  float alpha_r, alpha_i, beta_r, beta_i;
-  float lo_scale_inv;
-  int is_complex;
-  const DynParams *dyn;
-  int *status;
-};
+using KernelParams = GemmKernelParams;
 
 template <int KIND> __device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b,
                                                            uint32_t idesc, uint32_t acc) {
@@ -137,6 +125,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
   const uint32_t k_blocks = p.k_blocks;
+  const bool dbg = (p.debug != nullptr);
+  unsigned long long dbg_wait = 0, dbg_wait2 = 0;
 
   if (warp == 0) {
     // ================================================================ TMA producer
@@ -145,8 +135,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
         const uint32_t s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1u;
-        if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
-                            ptx::kErrWaitEmpty))
+        if (!ptx::mbar_wait_timed(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
+                                  ptx::kErrWaitEmpty, dbg, &dbg_wait))
           break;
         const uint32_t fb = ptx::smem_u32(&full_bar[s]);
         ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
@@ -162,6 +152,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_b, fb, kc, n0, za);
         }
       }
+      if (dbg) atomicAdd(p.debug + 2, dbg_wait);
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
@@ -169,15 +160,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const uint32_t d0 = tmem_base;
       const uint32_t d1 = tmem_base + D1_COL;
       bool ok = true;
+      const long long dbg_t0 = clock64();
       for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
         const uint32_t s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1u;
-        ok = ptx::mbar_wait(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
-                            ptx::kErrWaitFull);
+        ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                                  ptx::kErrWaitFull, dbg, &dbg_wait);
         if (!ok) break;
         // D0 of the previous stage must have been drained before it is overwritten.
-        ok = ptx::mbar_wait(ptx::smem_u32(d0_empty), (kb & 1u) ^ 1u, abort_flag, p.status,
-                            ptx::kErrWaitD0Empty);
+        ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (kb & 1u) ^ 1u, abort_flag, p.status,
+                                  ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
         if (!ok) break;
         ptx::tc_fence_after();
         const uint32_t st = ptx::smem_u32(smem + s * Cfg::STAGE_BYTES);
@@ -206,6 +198,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         ptx::tc_commit(ptx::smem_u32(&empty_bar[s]));
       }
       if (ok) ptx::tc_commit(ptx::smem_u32(d1_full));
+      if (dbg) {
+        atomicAdd(p.debug + 0, dbg_wait);
+        atomicAdd(p.debug + 1, dbg_wait2);
+        atomicAdd(p.debug + 4, static_cast<unsigned long long>(clock64() - dbg_t0));
+        atomicAdd(p.debug + 5, 1ull);
+      }
     }
   } else if (warp >= 4) {
     // ================================================================ drain + epilogue
@@ -220,8 +218,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     bool ok = true;
     for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-      ok = ptx::mbar_wait(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
-                          ptx::kErrWaitD0Full);
+      ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
+                                ptx::kErrWaitD0Full, dbg, &dbg_wait);
       if (!ok) break;
       ptx::tc_fence_after();
 #pragma unroll
@@ -237,6 +235,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(d0_empty));
     }
 
+    if (dbg && warp == 4 && lane == 0) atomicAdd(p.debug + 3, dbg_wait);
     if (ok && EC) {
       ok = ptx::mbar_wait(ptx::smem_u32(d1_full), 0u, abort_flag, p.status, ptx::kErrWaitD1Full);
       if (ok) {
@@ -304,13 +303,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
+} // namespace
+
 // ---------------------------------------------------------------- host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn get_encode_fn() {
+static EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, []() {
@@ -344,6 +345,8 @@ bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_
          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
+
+namespace {
 
 template <int KIND, int BN, bool EC>
 cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
@@ -382,6 +385,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   p.is_complex = a.is_complex ? 1 : 0;
   p.dyn = a.dyn;
   p.status = a.dev_status;
+  p.debug = a.debug;
   const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
   if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
   kernel<<<static_cast<unsigned>(grid), NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(map_a, map_b, p);

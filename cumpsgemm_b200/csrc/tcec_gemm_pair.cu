@@ -1,0 +1,338 @@
+// Error-corrected tensor-core GEMM, CTA-pair variant (tcgen05 cta_group::2).
+//
+// Same arithmetic, panels and barrier protocol as tcec_gemm.cu (which replaces the
+// reference's src/cumpsgemm_kernel.cuh:468-585); what changes is the tile.  A cluster of two
+// CTAs owns a 256 x 256 tile of C: each CTA loads its own 128 rows of A (hi, lo) and its own
+// 128-row half of the B tile (hi, lo), the even CTA issues every tcgen05.mma for the pair,
+// and each CTA's TMEM receives its own 128 x 256 part of the accumulators, which its own
+// epilogue warps drain.  Per SM and k-stage this moves 64 KiB from L2 instead of 96 KiB and
+// leaves room for three stages instead of two.
+//
+// Barriers (one set per CTA at identical shared-memory offsets; "leader" = cluster rank 0):
+//   full[s]   leader's only: 1 arrival (leader's producer, expect_tx of both CTAs' bytes);
+//             both CTAs' TMA loads complete on it (cta_group::2 loads, no multicast)
+//   empty[s]  in both CTAs: 1 arrival, tcgen05.commit multicast from the leader
+//   d0_full   in both CTAs: commit multicast after the hi*hi products of a stage
+//   d0_empty  leader's only: 16 arrivals = 8 drain warps of each CTA (remote mbarrier arrive)
+//   d1_full   in both CTAs: commit multicast after the last stage
+// Every wait is bounded; no TMA multicast is used.
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace cumpsgemm_b200 {
+namespace {
+
+constexpr int BM_CTA = 128;  // rows of C per CTA
+constexpr int BN_PAIR = 256; // columns of C per pair (each CTA stores 128 rows of B)
+constexpr int ROW_BYTES = kGemmRowBytes;
+constexpr int NUM_THREADS = 384;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t D1_COL = 256;
+constexpr int TILE_BYTES = 128 * ROW_BYTES;       // every sub-tile is 128 rows
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;       // A_hi, A_lo, B_hi, B_lo
+constexpr int STAGES = 3;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+template <int KIND>
+__device__ __forceinline__ void mma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
+                                         uint32_t acc) {
+  if constexpr (KIND == 0) {
+    ptx::mma_f16_ss_pair(d, a, b, idesc, acc);
+  } else {
+    ptx::mma_tf32_ss_pair(d, a, b, idesc, acc);
+  }
+}
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
+  constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
+  constexpr int BK = ROW_BYTES / ELEM_BYTES;
+  constexpr int K_STEPS = ROW_BYTES / 32;
+  constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
+  constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, 2 * BM_CTA, BN_PAIR);
+  constexpr int CPT = BN_PAIR / 2;
+
+  if (p.dyn != nullptr && p.dyn->gemm_mode != MY_MODE) return; // uniform over the cluster
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + STAGES;
+  uint64_t *d0_full = bars + 2 * STAGES;
+  uint64_t *d0_empty = bars + 2 * STAGES + 1;
+  uint64_t *d1_full = bars + 2 * STAGES + 2;
+  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const bool leader = (rank == 0);
+
+  // ---- pair-tile coordinates, grouped raster over pairs
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
+  const uint32_t batch_id = pair / tiles_per_batch;
+  const uint32_t t = pair - batch_id * tiles_per_batch;
+  constexpr uint32_t GROUP_M = 8;
+  const uint32_t tiles_in_group = GROUP_M * p.tiles_n;
+  const uint32_t group_id = t / tiles_in_group;
+  const uint32_t first_m = group_id * GROUP_M;
+  const uint32_t group_rows = min(p.tiles_m - first_m, GROUP_M);
+  const uint32_t in_group = t - group_id * tiles_in_group;
+  const uint32_t tile_m = first_m + in_group % group_rows;
+  const uint32_t tile_n = in_group / group_rows;
+  const int m0 = static_cast<int>(tile_m * 2 * BM_CTA + rank * BM_CTA); // this CTA's rows
+  const int n0 = static_cast<int>(tile_n * BN_PAIR);                    // the pair's columns
+  const int nb0 = n0 + static_cast<int>(rank) * 128;                    // this CTA's B rows
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(d0_full), 1);
+    ptx::mbar_init(ptx::smem_u32(d0_empty), 2 * NUM_EPI_WARPS);
+    ptx::mbar_init(ptx::smem_u32(d1_full), 1);
+    *abort_flag = 0;
+    ptx::mbar_init_fence();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_base_ptr), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must exist before any remote arrive / remote TMA completion
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_ptr;
+  const uint32_t k_blocks = p.k_blocks;
+  const bool dbg = (p.debug != nullptr);
+  unsigned long long dbg_wait = 0, dbg_wait2 = 0;
+
+  if (warp == 0) {
+    // ================================================================ TMA producer (both CTAs)
+    if (lane == 0) {
+      const int za = static_cast<int>(batch_id * 2u);
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        if (!ptx::mbar_wait_timed(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
+                                  ptx::kErrWaitEmpty, dbg, &dbg_wait))
+          break;
+        const uint32_t fb_local = ptx::smem_u32(&full_bar[s]);
+        if (leader) ptx::mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES);
+        const uint32_t fb = ptx::map_to_cta(fb_local, 0); // the leader's barrier
+        const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
+        const int kc = static_cast<int>(kb * BK);
+        ptx::tma_load_3d_pair(st, &map_a, fb, kc, m0, za);
+        ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, kc, m0, za + 1);
+        ptx::tma_load_3d_pair(st + 2 * TILE_BYTES, &map_b, fb, kc, nb0, za);
+        ptx::tma_load_3d_pair(st + 3 * TILE_BYTES, &map_b, fb, kc, nb0, za + 1);
+      }
+      if (dbg) atomicAdd(p.debug + 2, dbg_wait);
+    }
+  } else if (warp == 1) {
+    // ================================================================ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      const uint32_t d0 = tmem_base;
+      const uint32_t d1 = tmem_base + D1_COL;
+      constexpr uint16_t BOTH = 0x3;
+      bool ok = true;
+      const long long dbg_t0 = clock64();
+      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const uint32_t s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1u;
+        ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                                  ptx::kErrWaitFull, dbg, &dbg_wait);
+        if (!ok) break;
+        ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (kb & 1u) ^ 1u, abort_flag, p.status,
+                                  ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t a_hi = ptx::make_kmajor_desc<ROW_BYTES>(st);
+        const uint64_t a_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + TILE_BYTES);
+        const uint64_t b_hi = ptx::make_kmajor_desc<ROW_BYTES>(st + 2 * TILE_BYTES);
+        const uint64_t b_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + 3 * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < K_STEPS; ++ks)
+          mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC, ks > 0 ? 1u : 0u);
+        ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
+#pragma unroll
+        for (int ks = 0; ks < K_STEPS; ++ks)
+          mma_pair<KIND>(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < K_STEPS; ++ks)
+          mma_pair<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
+        ptx::tc_commit_pair(ptx::smem_u32(&empty_bar[s]), BOTH);
+      }
+      if (ok) ptx::tc_commit_pair(ptx::smem_u32(d1_full), BOTH);
+      if (dbg) {
+        atomicAdd(p.debug + 0, dbg_wait);
+        atomicAdd(p.debug + 1, dbg_wait2);
+        atomicAdd(p.debug + 4, static_cast<unsigned long long>(clock64() - dbg_t0));
+        atomicAdd(p.debug + 5, 1ull);
+      }
+    }
+  } else if (warp >= 4) {
+    // ================================================================ drain + epilogue (both CTAs)
+    const uint32_t quarter = static_cast<uint32_t>(warp & 3);
+    const uint32_t half = static_cast<uint32_t>((warp - 4) >> 2);
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const uint32_t col_base = half * CPT;
+    const uint32_t d0_empty_leader = ptx::map_to_cta(ptx::smem_u32(d0_empty), 0);
+
+    float acc[CPT];
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
+
+    bool ok = true;
+    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
+                                ptx::kErrWaitD0Full, dbg, &dbg_wait);
+      if (!ok) break;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int pc = 0; pc < CPT / 32; ++pc) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + col_base + pc * 32, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[pc * 32 + i] += __uint_as_float(v[i]);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(d0_empty_leader);
+    }
+
+    if (dbg && warp == 4 && lane == 0) atomicAdd(p.debug + 3, dbg_wait);
+    if (ok) {
+      ok = ptx::mbar_wait(ptx::smem_u32(d1_full), 0u, abort_flag, p.status, ptx::kErrWaitD1Full);
+      if (ok) {
+        ptx::tc_fence_after();
+        const float lsi = p.lo_scale_inv;
+#pragma unroll
+        for (int pc = 0; pc < CPT / 32; ++pc) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + D1_COL + lane_addr + col_base + pc * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            acc[pc * 32 + i] = fmaf(__uint_as_float(v[i]), lsi, acc[pc * 32 + i]);
+        }
+      }
+    }
+
+    if (ok) {
+      const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
+      const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
+      const float br = p.beta_r, bi = p.beta_i;
+      const bool read_c = (br != 0.f) || (bi != 0.f);
+      const uint32_t row = static_cast<uint32_t>(m0) + quarter * 32u + static_cast<uint32_t>(lane);
+      const bool row_ok = row < p.m;
+      float *cbase = p.c + static_cast<uint64_t>(batch_id) * p.stride_c + row;
+      const float sgn = (lane & 1) ? 1.f : -1.f;
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) {
+        const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i);
+        if (col < p.n) {
+          float *cp = cbase + static_cast<uint64_t>(col) * p.ldc;
+          float old = 0.f;
+          if (read_c && row_ok) old = *cp;
+          float out;
+          if (p.is_complex) {
+            const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
+            const float old_o = __shfl_xor_sync(0xffffffffu, old, 1);
+            out = ar * acc[i] + sgn * ai * acc_o;
+            if (read_c) out += br * old + sgn * bi * old_o;
+          } else {
+            out = ar * acc[i];
+            if (read_c) out = fmaf(br, old, out);
+          }
+          if (row_ok) *cp = out;
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  // The peer's shared memory and TMEM are in use by the leader's MMAs until d1_full has fired
+  // in both CTAs; the cluster barrier below keeps either CTA from leaving before the other
+  // has finished its epilogue.
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (*abort_flag) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
+  auto kernel = tcec_gemm_pair_kernel<KIND>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const uint32_t planes = a.batch * 2u;
+  CUtensorMap map_a, map_b;
+  if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, 128) ||
+      !make_panel_map(&map_b, a.kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, 128)) {
+    return cudaErrorInvalidValue;
+  }
+  GemmKernelParams p;
+  p.c = a.c;
+  p.ldc = a.ldc;
+  p.stride_c = a.stride_c;
+  p.m = a.m;
+  p.n = a.n;
+  const uint32_t es = (a.kind == SplitKind::fp16) ? 2u : 4u;
+  p.k_blocks = a.k_pad / (ROW_BYTES / es);
+  p.tiles_m = (a.m + 2 * BM_CTA - 1) / (2 * BM_CTA);
+  p.tiles_n = (a.n + BN_PAIR - 1) / BN_PAIR;
+  p.alpha_r = a.alpha_r;
+  p.alpha_i = a.alpha_i;
+  p.beta_r = a.beta_r;
+  p.beta_i = a.beta_i;
+  p.lo_scale_inv = (a.kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
+  p.is_complex = a.is_complex ? 1 : 0;
+  p.dyn = a.dyn;
+  p.status = a.dev_status;
+  p.debug = a.debug;
+  const uint64_t grid = 2ull * p.tiles_m * p.tiles_n * a.batch;
+  if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
+  if (a.rows_pad_a < p.tiles_m * 2 * BM_CTA || a.rows_pad_b < p.tiles_n * BN_PAIR)
+    return cudaErrorInvalidValue;
+  kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return cudaGetLastError();
+}
+
+} // namespace
+
+cudaError_t launch_tcec_gemm_pair(const TcecGemmArgs &a, cudaStream_t stream) {
+  if (!a.error_correction) return cudaErrorInvalidValue;
+  return (a.kind == SplitKind::fp16) ? launch_pair<0>(a, stream) : launch_pair<1>(a, stream);
+}
+
+} // namespace cumpsgemm_b200

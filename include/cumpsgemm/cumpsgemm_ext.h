@@ -133,6 +133,11 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
  * synchronises the stream, returns the number of launch groups since the last query and the
  * summed durations of the split passes and of the GEMM kernels, and clears the record.
  * In AUTO mode both gated kinds are recorded, the deselected one with near-zero time. */
+/* Optional stall breakdown of the GEMM kernels: eight 64-bit words in device memory that the
+ * kernels add to (cycles the MMA issuer waited for operands [0] and for the accumulator drain
+ * [1], the TMA producer for a free stage [2], one drain warp for a finished chunk [3], MMA
+ * loop cycles [4], contributing CTAs [5]).  NULL (default) disables it. */
+void cuMpSGEMM_set_debug_buffer(cuMpSGEMM_handle_t handle, unsigned long long *dev_words8);
 void cuMpSGEMM_set_kernel_timing(cuMpSGEMM_handle_t handle, int enable);
 unsigned long long cuMpSGEMM_get_kernel_timing(cuMpSGEMM_handle_t handle, double *split_ms,
                                                double *gemm_ms);

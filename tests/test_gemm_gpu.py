@@ -103,8 +103,12 @@ def test_sgemm_degenerate_shapes(handle, oracle, shape):
     assert oracle.residual(truth, res, m) < oracle.error_threshold(True, max(k, 16))
 
 
-@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("tile", [64, 128, 256, "256-single-cta"])
 def test_every_tile_width(handle, oracle, tile):
+    """All kernel variants: 128x64, 128x128, 256x256 on CTA pairs, 128x256 on one CTA."""
+    if tile == "256-single-cta":
+        tile = 256
+        os.environ["CUMPSGEMM_PAIR"] = "0"
     os.environ["CUMPSGEMM_TILE_N"] = str(tile)
     try:
         m, n, k = 384, 520, 200
@@ -112,8 +116,11 @@ def test_every_tile_width(handle, oracle, tile):
         assert oracle.residual(truth, res, m) < oracle.error_threshold(True, k)
         _, _, _, res, truth, _ = _run_real(handle, oracle, T, N, m, n, k, TF32TCEC, seed=6)
         assert oracle.residual(truth, res, m) < oracle.error_threshold(True, k)
+        r = _run_complex(handle, oracle, Cj, N, 130, 300, 70, FP16TCEC, 1.0 - 1.0j, 0.5j, seed=8)
+        assert r < oracle.error_threshold(True, 70)
     finally:
         os.environ.pop("CUMPSGEMM_TILE_N", None)
+        os.environ.pop("CUMPSGEMM_PAIR", None)
 
 
 def test_tile_choice_is_reported(handle, oracle):
