@@ -144,20 +144,15 @@ def cpu_gemm_sample(n_full: int, target_seconds: float, seed: int = 1):
 
     m = k = n_full
     rng = orc.rng(seed)
-    a = (rng.uniform(-1, 1, size=m * k).astype(np.float32))
-    cols_cal = 48
+    a = rng.uniform(-1, 1, size=m * k).astype(np.float32)
+    cols_cal = 96
     b = rng.uniform(-1, 1, size=k * cols_cal).astype(np.float32)
     c = np.zeros(m * cols_cal, dtype=np.float32)
+    orc.gemm_f32(0, 0, m, cols_cal, k, 1.0, a, m, b, k, 0.0, c, m)      # warm-up (threads, pages)
     t0 = time.perf_counter()
     orc.gemm_f32(0, 0, m, cols_cal, k, 1.0, a, m, b, k, 0.0, c, m)
-    t_cal = time.perf_counter() - t0          # includes packing A once
-    t0 = time.perf_counter()
-    orc.gemm_f32(0, 0, m, 2 * cols_cal, k, 1.0, a, m, np.concatenate([b, b]), k, 0.0,
-                 np.zeros(m * 2 * cols_cal, dtype=np.float32), m)
-    t_cal2 = time.perf_counter() - t0
-    per_col = max((t_cal2 - t_cal) / cols_cal, 1e-6)
-    fixed = max(t_cal - per_col * cols_cal, 0.0)
-    cols = int(max(cols_cal, min(n_full, (target_seconds - fixed) / per_col)))
+    per_col = max((time.perf_counter() - t0) / cols_cal, 1e-7)
+    cols = int(max(cols_cal, min(n_full, target_seconds / per_col)))
     cols = max(6, cols // 6 * 6)
     b = rng.uniform(-1, 1, size=k * cols).astype(np.float32)
     c = np.zeros(m * cols, dtype=np.float32)
@@ -179,8 +174,8 @@ def run_reference(args, rank, world):
     cores = host_cores()
     rng = orc.rng(1)
     a = rng.uniform(-1, 1, size=m * k).astype(np.float32)
-    # size one step at about 4 s
-    tf, dt, cols = cpu_gemm_sample(n_full, 4.0)
+    # size one step at about 3 s
+    tf, dt, cols = cpu_gemm_sample(n_full, 3.0)
     b = rng.uniform(-1, 1, size=k * cols).astype(np.float32)
     c = rng.uniform(-1, 1, size=m * cols).astype(np.float32)
     for _ in range(args.warmup):
@@ -335,7 +330,7 @@ def run_ours(args, rank, local_rank, world):
         tf, dt, cols = cpu_gemm_sample(n, 15.0)
         cpu = {"value": tf, "unit": UNIT, "cores": host_cores(), "kind": "port",
                "sample": f"FP32 host GEMM on {cols} of {n} columns of an m=k={n} problem "
-                         f"({dt:.1f} s, A packed inside the timed call)"}
+                         f"({dt:.1f} s)"}
 
     if rank == 0:
         line = {

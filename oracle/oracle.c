@@ -164,44 +164,57 @@ static void micro_kernel(size_t kb, const float *ap /* kb x MR packed */, const 
   }
 }
 
+#define MC 192 /* rows of A packed per block (MC x KB floats = 288 KiB, sized for L2) */
+
 void oracle_sgemm_f32(int op_a, int op_b, size_t m, size_t n, size_t k, float alpha,
                       const float *a, size_t lda, const float *b, size_t ldb, float beta, float *c,
                       size_t ldc) {
-  const size_t mp = (m + MR - 1) / MR; /* row panels */
-  /* packed A: panel p, k index l, row r  ->  ap[(p * k + l) * MR + r], zero padded */
-  float *ap = (float *)aligned_alloc(64, sizeof(float) * mp * k * MR);
-#pragma omp parallel for schedule(static)
-  for (size_t p = 0; p < mp; ++p)
-    for (size_t l = 0; l < k; ++l)
-      for (size_t r = 0; r < MR; ++r) {
-        const size_t i = p * MR + r;
-        ap[(p * k + l) * MR + r] = (i < m) ? lda_at(a, op_a, i, l, lda) : 0.f;
-      }
   const size_t b_l = (op_b == OP_N) ? 1 : ldb;
   const size_t b_j = (op_b == OP_N) ? ldb : 1;
-  const size_t njb = (n + NR - 1) / NR;
-#pragma omp parallel for schedule(dynamic, 8)
-  for (size_t jb = 0; jb < njb; ++jb) {
-    const size_t j0 = jb * NR;
-    const size_t nr = (n - j0 < NR) ? (n - j0) : NR;
+  const size_t nib = (m + MC - 1) / MC;
+  /* Each thread owns row blocks of C: it packs one MC x KB block of op(A) into a private
+   * buffer (16-row panels, zero padded), sweeps all columns with the micro-kernel and
+   * accumulates into C, k-block after k-block.  A is read once, B once per row block. */
+#pragma omp parallel
+  {
+    float *ap = (float *)aligned_alloc(64, sizeof(float) * MC * KB);
     float acc[NR * MR] __attribute__((aligned(32)));
-    for (size_t p = 0; p < mp; ++p) {
-      for (size_t x = 0; x < NR * MR; ++x) acc[x] = 0.f;
+#pragma omp for schedule(dynamic, 1)
+    for (size_t ib = 0; ib < nib; ++ib) {
+      const size_t i0 = ib * MC;
+      const size_t mb = (m - i0 < MC) ? (m - i0) : MC;
+      const size_t np = (mb + MR - 1) / MR;
       for (size_t l0 = 0; l0 < k; l0 += KB) {
         const size_t kb = (k - l0 < KB) ? (k - l0) : KB;
-        micro_kernel(kb, ap + (p * k + l0) * MR, b + l0 * b_l + j0 * b_j, b_l, b_j, nr, acc);
-      }
-      for (size_t j = 0; j < nr; ++j)
-        for (size_t r = 0; r < MR; ++r) {
-          const size_t i = p * MR + r;
-          if (i >= m) break;
-          float *cp = c + i + (j0 + j) * ldc;
-          const float base = (beta == 0.f) ? 0.f : beta * (*cp);
-          *cp = alpha * acc[j * MR + r] + base;
+        for (size_t p = 0; p < np; ++p)
+          for (size_t l = 0; l < kb; ++l)
+            for (size_t r = 0; r < MR; ++r) {
+              const size_t i = i0 + p * MR + r;
+              ap[(p * kb + l) * MR + r] = (i < i0 + mb) ? lda_at(a, op_a, i, l0 + l, lda) : 0.f;
+            }
+        for (size_t j0 = 0; j0 < n; j0 += NR) {
+          const size_t nr = (n - j0 < NR) ? (n - j0) : NR;
+          for (size_t p = 0; p < np; ++p) {
+            for (size_t x = 0; x < NR * MR; ++x) acc[x] = 0.f;
+            micro_kernel(kb, ap + p * kb * MR, b + l0 * b_l + j0 * b_j, b_l, b_j, nr, acc);
+            for (size_t j = 0; j < nr; ++j)
+              for (size_t r = 0; r < MR; ++r) {
+                const size_t i = i0 + p * MR + r;
+                if (i >= i0 + mb) break;
+                float *cp = c + i + (j0 + j) * ldc;
+                if (l0 == 0) {
+                  const float base = (beta == 0.f) ? 0.f : beta * (*cp);
+                  *cp = alpha * acc[j * MR + r] + base;
+                } else {
+                  *cp += alpha * acc[j * MR + r];
+                }
+              }
+          }
         }
+      }
     }
+    free(ap);
   }
-  free(ap);
 }
 
 /* complex64 FP32 GEMM, four real products, interleaved storage */
