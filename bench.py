@@ -358,6 +358,110 @@ def run_ours(args, rank, local_rank, world):
     handle.destroy()
 
 
+def run_sweep(args):
+    """Documentation runs for the other benchmark configurations (one JSON line each, marked
+    "sweep": true): square SGEMM sweep in both kinds, the wide-exponent SCALING / AUTO case,
+    the strided-batch complex case, and the bandwidth of the statistics / scaling kernels."""
+    import torch
+
+    from cumpsgemm_b200 import api
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    h = api.Handle()
+    h.use_current_torch_stream()
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)
+    hbm = None
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        hbm = float(json.loads(pk.read_text())["hbm_gbs"])
+
+    def timeit(fn, iters):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def emit(**kw):
+        kw["sweep"] = True
+        print(json.dumps(kw), flush=True)
+
+    def uexp(count, lo, hi):
+        u = torch.rand(count, device=dev, generator=g) * 2 - 1
+        e = torch.randint(lo, hi + 1, (count,), device=dev, generator=g, dtype=torch.int32)
+        return torch.ldexp(u, e)
+
+    # config 1 and 2: square SGEMM
+    for n in (1024, 2048, 4096, 8192, 16384):
+        a, b = uexp(n * n, -8, 8), uexp(n * n, -8, 8)
+        c = torch.rand(n * n, device=dev, generator=g) * 2 - 1
+        for mode in ("FP16TCEC", "TF32TCEC"):
+            ms = timeit(lambda: h.gemm(0, 0, n, n, n, 1.0, a, n, b, n, 0.5, c, n,
+                                       api.ComputeMode[mode]), 20 if n <= 8192 else 5)
+            emit(config=f"sgemm {mode} m=n=k={n} beta=0.5", ms=ms, tflops=2.0 * n ** 3 / ms / 1e9)
+        del a, b, c
+    # config 3: wide exponent range, 8192^3, SCALING and AUTO; statistics / scaling bandwidth
+    n = 8192
+    sgn = torch.where(torch.rand(n * n, device=dev, generator=g) < 0.5, -1.0, 1.0)
+    a = torch.ldexp(sgn * (1 + torch.rand(n * n, device=dev, generator=g)),
+                    torch.randint(-30, 11, (n * n,), device=dev, generator=g, dtype=torch.int32))
+    b = a.flip(0).contiguous()
+    c = torch.zeros(n * n, device=dev)
+    for mode in ("FP16TCEC_SCALING", "AUTO"):
+        lib_mode = api.ComputeMode[mode]
+        if mode == "AUTO":
+            def call():
+                ia = h.exp_stats_ext(n, n, a, n)
+                ib = h.exp_stats_ext(n, n, b, n)
+                h.gemm_strided_batch_with_stats(0, 0, n, n, n, 1.0, a, n, 0, b, n, 0, 0.0, c, n, 0,
+                                                1, lib_mode, ia, ib)
+        else:
+            def call():
+                h.gemm(0, 0, n, n, n, 1.0, a, n, b, n, 0.0, c, n, lib_mode)
+        ms = timeit(call, 10)
+        emit(config=f"sgemm {mode} m=n=k={n} exponents in [-30,10] (statistics + fused scaling + GEMM)",
+             ms=ms, tflops=2.0 * n ** 3 / ms / 1e9)
+    nbytes = n * n * 4
+    for name, fn, traffic in (
+            ("exp_stats_ext (stage 1 + stage 2, wide range)", lambda: h.exp_stats_ext(n, n, a, n), 2 * nbytes),
+            ("exp_max_ext", lambda: h.exp_max_ext(n, n, a, n), nbytes),
+            ("scale_A then reset_scale_A (in place, read + write each)",
+             lambda: (h.scale_A(sid, 1, n, n, c2, n), h.reset_scale_A(sid, 1, n, n, c2, n)), 4 * nbytes)):
+        if name.startswith("scale"):
+            c2 = torch.rand(n * n, device=dev, generator=g) + 1
+            sid = h.exp_max_ext(n, n, c2, n)
+        ms = timeit(fn, 20)
+        gbs = traffic / ms / 1e6
+        emit(config=f"{name} on {n}x{n} FP32", ms=ms, gbs=gbs,
+             frac_of_measured_hbm=(gbs / hbm if hbm else None))
+    del a, b, c
+    # config 4: strided-batch complex GEMM, unit-Frobenius operands, SCALING
+    batch, s = 512, 256
+    za = torch.randn(batch, s * s, device=dev, generator=g, dtype=torch.float32) + \
+        1j * torch.randn(batch, s * s, device=dev, generator=g, dtype=torch.float32)
+    zb = torch.randn(batch, s * s, device=dev, generator=g, dtype=torch.float32) + \
+        1j * torch.randn(batch, s * s, device=dev, generator=g, dtype=torch.float32)
+    za = (za / za.abs().pow(2).sum(1, keepdim=True).sqrt()).to(torch.complex64).contiguous()
+    zb = (zb / zb.abs().pow(2).sum(1, keepdim=True).sqrt()).to(torch.complex64).contiguous()
+    zc = torch.zeros(batch * s * s, dtype=torch.complex64, device=dev)
+    for mode in ("FP16TCEC", "FP16TCEC_SCALING"):
+        ms = timeit(lambda: h.gemm_strided_batch(0, 0, s, s, s, 1.0, za, s, s * s, zb, s, s * s, 0.0,
+                                                 zc, s, s * s, batch, api.ComputeMode[mode]), 20)
+        emit(config=f"cgemm strided batch {mode} batch={batch} m=n=k={s}", ms=ms,
+             tflops=8.0 * batch * s ** 3 / ms / 1e9)
+    # config 5a, one GPU's share at 8 GPUs: batch 8 of 8192^3, AUTO decided per call
+    status = h.kernel_status()
+    emit(config="kernel status after sweep", status=status)
+    h.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -369,10 +473,15 @@ def main():
     ap.add_argument("--beta", type=float, default=0.5)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="run the other benchmark configurations (documentation runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

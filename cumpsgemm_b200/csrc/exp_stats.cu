@@ -22,7 +22,7 @@ namespace cumpsgemm_b200 {
 namespace {
 
 constexpr int THREADS = 256;
-constexpr int CHUNK = 4096; // floats of one column handled per work item
+constexpr int CHUNK = 16384; // floats of one column handled per work item
 
 struct ScanParams {
   const float *ptr;   // complex input viewed as floats
@@ -63,9 +63,11 @@ ScanParams make_scan(const void *ptr, uint64_t m, uint64_t n, uint64_t ld, uint3
   return s;
 }
 
+// Per-thread partial results.  32-bit counters are enough: one thread visits fewer than
+// 2^32 values; they are widened before the cross-thread reduction.
 struct Acc {
   float max_abs;
-  unsigned long long total, underflow;
+  unsigned int total, underflow;
 };
 
 template <bool COUNT, bool MAXV>
@@ -94,7 +96,22 @@ __device__ __forceinline__ void scan_items(const ScanParams &s, Acc &a, float ig
     if (s.vec_ok) {
       // begin is a multiple of 4 and the column start is 16-byte aligned
       const uint64_t vec_end = begin + ((end - begin) & ~3ull);
-      for (uint64_t i = begin + threadIdx.x * 4ull; i < vec_end; i += THREADS * 4ull) {
+      uint64_t i = begin + threadIdx.x * 4ull;
+      // four independent 16-byte loads in flight per thread
+      for (; i + 3ull * THREADS * 4ull < vec_end; i += 4ull * THREADS * 4ull) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[u] = *reinterpret_cast<const float4 *>(p + i + static_cast<uint64_t>(u) * THREADS * 4ull);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          visit<COUNT, MAXV>(v[u].x, a, ignore_thr, uf_thr);
+          visit<COUNT, MAXV>(v[u].y, a, ignore_thr, uf_thr);
+          visit<COUNT, MAXV>(v[u].z, a, ignore_thr, uf_thr);
+          visit<COUNT, MAXV>(v[u].w, a, ignore_thr, uf_thr);
+        }
+      }
+      for (; i < vec_end; i += THREADS * 4ull) {
         const float4 v = *reinterpret_cast<const float4 *>(p + i);
         visit<COUNT, MAXV>(v.x, a, ignore_thr, uf_thr);
         visit<COUNT, MAXV>(v.y, a, ignore_thr, uf_thr);
@@ -111,9 +128,13 @@ __device__ __forceinline__ void scan_items(const ScanParams &s, Acc &a, float ig
 }
 
 template <bool COUNT, bool MAXV>
-__device__ __forceinline__ void reduce_and_publish(Acc a, float *max_slot,
+__device__ __forceinline__ void reduce_and_publish(Acc acc, float *max_slot,
                                                    unsigned long long *total_slot,
                                                    unsigned long long *uf_slot) {
+  struct {
+    float max_abs;
+    unsigned long long total, underflow;
+  } a{acc.max_abs, acc.total, acc.underflow};
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) {
     if (MAXV) a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, off));
@@ -161,7 +182,7 @@ __global__ void init_slot_kernel(float *max_slot, unsigned long long *total_slot
 __global__ void __launch_bounds__(THREADS)
     stage1_kernel(const ScanParams s, float *max_slot, unsigned long long *total_slot,
                   unsigned long long *uf_slot, float ignore_thr, float uf_thr) {
-  Acc a{0.f, 0ull, 0ull};
+  Acc a{0.f, 0u, 0u};
   scan_items<true, true>(s, a, ignore_thr, uf_thr);
   reduce_and_publish<true, true>(a, max_slot, total_slot, uf_slot);
 }
@@ -185,7 +206,7 @@ __global__ void __launch_bounds__(THREADS)
                   float half_ignore_thr, float half_uf_thr) {
   if (*mode != CUMPSGEMM_UNDEFINED) return; // launch-and-exit
   const float mx = *max_slot;
-  Acc a{0.f, 0ull, 0ull};
+  Acc a{0.f, 0u, 0u};
   scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx);
   reduce_and_publish<true, false>(a, nullptr, total_slot, uf_slot);
 }
@@ -201,7 +222,7 @@ __global__ void decide2_kernel(int *mode, const unsigned long long *total_slot,
 }
 
 __global__ void __launch_bounds__(THREADS) max_only_kernel(const ScanParams s, float *max_slot) {
-  Acc a{0.f, 0ull, 0ull};
+  Acc a{0.f, 0u, 0u};
   scan_items<false, true>(s, a, 0.f, 0.f);
   reduce_and_publish<false, true>(a, max_slot, nullptr, nullptr);
 }

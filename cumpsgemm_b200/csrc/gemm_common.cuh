@@ -25,6 +25,8 @@ struct GemmKernelParams {
   // and for the accumulator drain [1], the producer for a free stage [2], drain warp 4 for
   // a finished chunk [3]; MMA loop cycles [4]; contributing CTAs [5].
   unsigned long long *debug;
+  // Stages whose hi*hi products accumulate in TMEM before one drain (pair kernel; 1 or 2).
+  uint32_t drain_chunk;
 };
 
 // Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {128 bytes of K, box_rows, 1},

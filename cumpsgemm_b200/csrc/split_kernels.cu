@@ -159,6 +159,138 @@ __global__ void __launch_bounds__(THREADS) split_kernel(const SplitParams p) {
   }
 }
 
+// ---------------------------------------------------------------- vectorised real paths
+// Used when the source base address, leading dimension and batch stride are multiples of
+// 16 bytes; anything else (and every complex operand) takes split_kernel above.
+
+template <int KIND>
+__device__ __forceinline__ void convert_store8(const float (&v)[8], void *panel, uint64_t off,
+                                               uint64_t plane_elems, uint32_t planes) {
+  if constexpr (KIND == 0) {
+    __align__(16) __half hi[8];
+    __align__(16) __half lo[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      hi[j] = __float2half_rn(v[j]);
+      lo[j] = __float2half_rn((v[j] - __half2float(hi[j])) * 2048.f);
+    }
+    __half *ph = reinterpret_cast<__half *>(panel) + off;
+    *reinterpret_cast<uint4 *>(ph) = *reinterpret_cast<const uint4 *>(hi);
+    if (planes == 2)
+      *reinterpret_cast<uint4 *>(ph + plane_elems) = *reinterpret_cast<const uint4 *>(lo);
+  } else {
+    __align__(16) float hi[8];
+    __align__(16) float lo[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      hi[j] = to_tf32(v[j]);
+      lo[j] = to_tf32(v[j] - hi[j]);
+    }
+    float *ph = reinterpret_cast<float *>(panel) + off;
+    reinterpret_cast<uint4 *>(ph)[0] = reinterpret_cast<const uint4 *>(hi)[0];
+    reinterpret_cast<uint4 *>(ph)[1] = reinterpret_cast<const uint4 *>(hi)[1];
+    if (planes == 2) {
+      reinterpret_cast<uint4 *>(ph + plane_elems)[0] = reinterpret_cast<const uint4 *>(lo)[0];
+      reinterpret_cast<uint4 *>(ph + plane_elems)[1] = reinterpret_cast<const uint4 *>(lo)[1];
+    }
+  }
+}
+
+// float4 at p if the whole vector is inside [.., limit), element-wise with zero fill otherwise
+__device__ __forceinline__ float4 load4_guarded(const float *p, uint64_t first, uint64_t limit,
+                                                bool row_ok) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!row_ok) return v;
+  if (first + 4 <= limit) return *reinterpret_cast<const float4 *>(p);
+  if (first + 0 < limit) v.x = p[0];
+  if (first + 1 < limit) v.y = p[1];
+  if (first + 2 < limit) v.z = p[2];
+  return v;
+}
+
+// Source is K-contiguous (element (r, kk) at [kk + r*ld]): no transpose, no shared memory.
+// CTA = 128 rows x 64 k; thread = 4 rows x 8 consecutive k, all eight 16-byte loads first.
+template <int KIND>
+__global__ void __launch_bounds__(THREADS) split_kcontig_kernel(const SplitParams p) {
+  constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
+  float scale = 1.f;
+  if (p.dyn != nullptr) {
+    if (p.dyn->gemm_mode != MY_MODE) return;
+    scale = (p.operand == 0) ? p.dyn->scale_a : p.dyn->scale_b;
+  }
+  const uint32_t b = blockIdx.z;
+  const float *src = p.src + static_cast<uint64_t>(b) * p.stride;
+  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * 64 + (threadIdx.x & 7) * 8;
+  const uint64_t r_base = static_cast<uint64_t>(blockIdx.y) * 128 + (threadIdx.x >> 3);
+  const uint64_t plane_elems = static_cast<uint64_t>(p.rows_pad) * p.k_pad;
+  float4 x[4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint64_t r = r_base + i * 32;
+    const bool row_ok = r < p.rows;
+    const float *q = src + r * p.ld + k0;
+    x[i][0] = load4_guarded(q, k0, p.k, row_ok);
+    x[i][1] = load4_guarded(q + 4, k0 + 4, p.k, row_ok);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint64_t r = r_base + i * 32;
+    if (r >= p.rows_pad) continue;
+    const float v[8] = {x[i][0].x * scale, x[i][0].y * scale, x[i][0].z * scale, x[i][0].w * scale,
+                        x[i][1].x * scale, x[i][1].y * scale, x[i][1].z * scale, x[i][1].w * scale};
+    convert_store8<KIND>(v, p.panel,
+                         static_cast<uint64_t>(b) * p.planes * plane_elems + r * p.k_pad + k0,
+                         plane_elems, p.planes);
+  }
+}
+
+// Source is row-contiguous (element (r, kk) at [r + kk*ld]): 64 x 64 transpose through
+// shared memory with 16-byte loads along r.
+template <int KIND>
+__global__ void __launch_bounds__(THREADS) split_rcontig_kernel(const SplitParams p) {
+  constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
+  float scale = 1.f;
+  if (p.dyn != nullptr) {
+    if (p.dyn->gemm_mode != MY_MODE) return;
+    scale = (p.operand == 0) ? p.dyn->scale_a : p.dyn->scale_b;
+  }
+  __shared__ float tile[TILE][TILE + 1];
+  const uint32_t b = blockIdx.z;
+  const float *src = p.src + static_cast<uint64_t>(b) * p.stride;
+  const uint64_t r0 = static_cast<uint64_t>(blockIdx.y) * TILE;
+  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * TILE;
+  const int r4 = (threadIdx.x & 15) * 4;
+  const int kq = threadIdx.x >> 4; // 0..15
+  float4 x[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint64_t gk = k0 + kq + i * 16;
+    x[i] = load4_guarded(src + gk * p.ld + r0 + r4, r0 + r4, p.rows, gk < p.k);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int kk = kq + i * 16;
+    tile[r4 + 0][kk] = x[i].x * scale;
+    tile[r4 + 1][kk] = x[i].y * scale;
+    tile[r4 + 2][kk] = x[i].z * scale;
+    tile[r4 + 3][kk] = x[i].w * scale;
+  }
+  __syncthreads();
+  const uint64_t plane_elems = static_cast<uint64_t>(p.rows_pad) * p.k_pad;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int er = (threadIdx.x >> 3) + it * 32;
+    const int ek = (threadIdx.x & 7) * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = tile[er][ek + j];
+    convert_store8<KIND>(v, p.panel,
+                         static_cast<uint64_t>(b) * p.planes * plane_elems + (r0 + er) * p.k_pad +
+                             k0 + ek,
+                         plane_elems, p.planes);
+  }
+}
+
 template <int KIND, int MODE> cudaError_t launch(const SplitArgs &a, cudaStream_t stream) {
   SplitParams p;
   p.src = reinterpret_cast<const float *>(a.src);
@@ -176,6 +308,19 @@ template <int KIND, int MODE> cudaError_t launch(const SplitArgs &a, cudaStream_
   p.src_k_contig = a.src_k_contig ? 1 : 0;
   const dim3 grid(a.k_pad / TILE, a.rows_pad / TILE, a.batch);
   if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidValue;
+  if constexpr (MODE == 0) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a.src) & 15u) == 0) && (a.ld % 4 == 0) &&
+                         (a.stride % 4 == 0);
+    if (aligned) {
+      if (a.src_k_contig) {
+        const dim3 g2(a.k_pad / 64, (a.rows_pad + 127) / 128, a.batch);
+        split_kcontig_kernel<KIND><<<g2, THREADS, 0, stream>>>(p);
+      } else {
+        split_rcontig_kernel<KIND><<<grid, THREADS, 0, stream>>>(p);
+      }
+      return cudaGetLastError();
+    }
+  }
   split_kernel<KIND, MODE><<<grid, THREADS, 0, stream>>>(p);
   return cudaGetLastError();
 }

@@ -149,15 +149,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       constexpr uint16_t BOTH = 0x3;
       bool ok = true;
       const long long dbg_t0 = clock64();
+      const uint32_t chunk = p.drain_chunk;
+      uint32_t chunk_idx = 0, in_chunk = 0;
       for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
         const uint32_t s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1u;
         ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
                                   ptx::kErrWaitFull, dbg, &dbg_wait);
         if (!ok) break;
-        ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (kb & 1u) ^ 1u, abort_flag, p.status,
-                                  ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
-        if (!ok) break;
+        if (in_chunk == 0) {
+          // D0 of the previous chunk must have been drained before it is overwritten.
+          ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (chunk_idx & 1u) ^ 1u, abort_flag,
+                                    p.status, ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
+          if (!ok) break;
+        }
         ptx::tc_fence_after();
         const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
         const uint64_t a_hi = ptx::make_kmajor_desc<ROW_BYTES>(st);
@@ -166,8 +171,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         const uint64_t b_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + 3 * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < K_STEPS; ++ks)
-          mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC, ks > 0 ? 1u : 0u);
-        ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
+          mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
+                         (in_chunk > 0 || ks > 0) ? 1u : 0u);
+        const bool last_in_chunk = (in_chunk + 1 == chunk) || (kb + 1 == k_blocks);
+        if (last_in_chunk) ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
 #pragma unroll
         for (int ks = 0; ks < K_STEPS; ++ks)
           mma_pair<KIND>(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
@@ -175,6 +182,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         for (int ks = 0; ks < K_STEPS; ++ks)
           mma_pair<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
         ptx::tc_commit_pair(ptx::smem_u32(&empty_bar[s]), BOTH);
+        if (last_in_chunk) {
+          in_chunk = 0;
+          ++chunk_idx;
+        } else {
+          ++in_chunk;
+        }
       }
       if (ok) ptx::tc_commit_pair(ptx::smem_u32(d1_full), BOTH);
       if (dbg) {
@@ -197,7 +210,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
 
     bool ok = true;
-    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+    const uint32_t n_chunks = (k_blocks + p.drain_chunk - 1) / p.drain_chunk;
+    for (uint32_t kb = 0; kb < n_chunks; ++kb) { // kb counts drains here
       ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
                                 ptx::kErrWaitD0Full, dbg, &dbg_wait);
       if (!ok) break;
@@ -320,6 +334,14 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   p.dyn = a.dyn;
   p.status = a.dev_status;
   p.debug = a.debug;
+  {
+    const char *e = std::getenv("CUMPSGEMM_DRAIN_CHUNK");
+    const int v = (e != nullptr) ? std::atoi(e) : 0;
+    // Default: two stages (128 FP16 / 64 TF32 k values) per drain.  Measured at m=n=k=16384,
+    // uniform(-1,1): residual 3.1e-7 / 2.8e-7 / 3.7e-7 / 6.5e-7 / 2.5e-6 / 1.9e-5 for 1 / 2 / 4 /
+    // 8 / 32 / 256 stages per drain (FP32 cuBLAS SGEMM on the same inputs: 2.3e-6).
+    p.drain_chunk = (v >= 1) ? static_cast<uint32_t>(v) : 2u;
+  }
   const uint64_t grid = 2ull * p.tiles_m * p.tiles_n * a.batch;
   if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
   if (a.rows_pad_a < p.tiles_m * 2 * BM_CTA || a.rows_pad_b < p.tiles_n * BN_PAIR)
