@@ -322,7 +322,8 @@ def run_ours(args, rank, local_rank, world):
         e2e = {"value": 2.0 * m * (n_local * world) * k / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                "steps": args.e2e_steps,
-               "note": "per rank: A, B, C copied from pinned host memory, C copied back; "
+               "note": "per rank: api.HostGemm, A, B, C copied from pinned host memory and C "
+                       "copied back inside the timed region, pipelined over 8 column blocks; "
                        "no NCCL broadcast on this leg"}
 
     cpu = None

@@ -85,6 +85,7 @@ PROTOTYPES = {
                                                        C.POINTER(C.c_ulonglong)]),
     "cuMpSGEMM_sgemm_module": (i32, _GEMM_ARGS + [C.POINTER(u32)]),
     "cuMpSGEMM_get_kernel_status": (i32, [vp]),
+    "cuMpSGEMM_selftest_bounded_wait": (i32, [vp, u32, C.POINTER(C.c_double)]),
     "cuMpSGEMM_set_workspace_limit": (None, [vp, C.c_size_t]),
     "cuMpSGEMM_set_debug_buffer": (None, [vp, vp]),
     "cuMpSGEMM_set_kernel_timing": (None, [vp, i32]),

@@ -194,6 +194,12 @@ class Handle:
         """Synchronise and return (then clear) the GEMM kernel's bounded-wait status word."""
         return self._lib.cuMpSGEMM_get_kernel_status(self._h)
 
+    def selftest_bounded_wait(self, limit_ms: int = 200) -> Tuple[int, float]:
+        """(status code, milliseconds waited) of a wait on a barrier nothing signals."""
+        t = C.c_double(0)
+        st = self._lib.cuMpSGEMM_selftest_bounded_wait(self._h, limit_ms, C.byref(t))
+        return st, t.value
+
     def set_workspace_limit(self, nbytes: int) -> None:
         self._lib.cuMpSGEMM_set_workspace_limit(self._h, nbytes)
 
@@ -398,18 +404,27 @@ def matmul(handle: Handle, A, B, mode: int = ComputeMode.FP16TCEC, out=None, alp
 class HostGemm:
     """GEMM on operands that live in (pinned) host memory.
 
-    Each call copies A, B (and C when beta != 0) to the device on the handle's stream, runs
-    the GEMM and copies C back; device staging buffers are kept between calls.  This is the
-    path a caller takes whose matrices are not resident on the GPU, e.g. a host BLAS client.
+    Each call copies A, B (and C when beta != 0) to the device, runs the GEMM and copies C
+    back; device staging buffers are kept between calls.  This is the path a caller takes
+    whose matrices are not resident on the GPU, e.g. a host BLAS client.
+
+    With op_B == N the call is pipelined over column blocks of B and C: A is uploaded first,
+    then for every block the upload of B_j / C_j (copy-in stream), the GEMM of the block (the
+    handle's stream) and the download of C_j (copy-out stream) overlap, so that the call
+    costs about the host-to-device transfer time alone.  The call is stream-ordered on the
+    stream current at call time: work queued after it on that stream sees the result in
+    C_host once that stream reaches it.
     """
 
-    def __init__(self, handle: Handle, device=None):
+    def __init__(self, handle: Handle, device=None, column_blocks: int = 8):
         import torch
 
         self.handle = handle
         self.torch = torch
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.column_blocks = max(1, int(column_blocks))
         self._bufs = {}
+        self._streams = None
 
     def _staging(self, key, host_tensor):
         t = self._bufs.get(key)
@@ -420,17 +435,59 @@ class HostGemm:
 
     def gemm(self, op_A, op_B, m, n, k, alpha, A_host, lda, B_host, ldb, beta, C_host, ldc, mode):
         """Returns (bytes copied host->device, bytes copied device->host)."""
+        torch = self.torch
         dA = self._staging("A", A_host)
         dB = self._staging("B", B_host)
         dC = self._staging("C", C_host)
-        h2d = 0
-        dA.copy_(A_host.reshape(-1), non_blocking=True)
-        dB.copy_(B_host.reshape(-1), non_blocking=True)
-        h2d += A_host.numel() * A_host.element_size() + B_host.numel() * B_host.element_size()
-        if complex(beta) != 0:
-            dC.copy_(C_host.reshape(-1), non_blocking=True)
-            h2d += C_host.numel() * C_host.element_size()
-        self.handle.gemm(op_A, op_B, m, n, k, alpha, dA, lda, dB, ldb, beta, dC, ldc, mode)
-        C_host.reshape(-1).copy_(dC, non_blocking=True)
-        d2h = C_host.numel() * C_host.element_size()
+        a_flat, b_flat, c_flat = A_host.reshape(-1), B_host.reshape(-1), C_host.reshape(-1)
+        need_c = complex(beta) != 0
+        es = A_host.element_size()
+        h2d = (a_flat.numel() + b_flat.numel() + (c_flat.numel() if need_c else 0)) * es
+        d2h = c_flat.numel() * es
+        blocks = self.column_blocks if (op_B == CUBLAS_OP_N and n >= 2 * self.column_blocks) else 1
+        if blocks == 1:
+            dA.copy_(a_flat, non_blocking=True)
+            dB.copy_(b_flat, non_blocking=True)
+            if need_c:
+                dC.copy_(c_flat, non_blocking=True)
+            self.handle.gemm(op_A, op_B, m, n, k, alpha, dA, lda, dB, ldb, beta, dC, ldc, mode)
+            c_flat.copy_(dC, non_blocking=True)
+            return h2d, d2h
+
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(device=self.device),
+                             torch.cuda.Stream(device=self.device),
+                             torch.cuda.Stream(device=self.device))
+        s_in, s_run, s_out = self._streams
+        caller = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(caller)
+        for st in (s_in, s_run, s_out):
+            st.wait_event(start)
+        self.handle.set_stream(s_run)
+        with torch.cuda.stream(s_in):
+            dA.copy_(a_flat, non_blocking=True)
+        per = -(-n // blocks)
+        for j0 in range(0, n, per):
+            j1 = min(n, j0 + per)
+            bs, be = j0 * ldb, min(b_flat.numel(), j1 * ldb)
+            cs, ce = j0 * ldc, min(c_flat.numel(), j1 * ldc)
+            with torch.cuda.stream(s_in):
+                dB[bs:be].copy_(b_flat[bs:be], non_blocking=True)
+                if need_c:
+                    dC[cs:ce].copy_(c_flat[cs:ce], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            s_run.wait_event(ready)
+            self.handle.gemm(op_A, op_B, m, j1 - j0, k, alpha, dA, lda, dB[bs:], ldb, beta, dC[cs:],
+                             ldc, mode)
+            done = torch.cuda.Event()
+            done.record(s_run)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                c_flat[cs:ce].copy_(dC[cs:ce], non_blocking=True)
+        finished = torch.cuda.Event()
+        finished.record(s_out)
+        caller.wait_event(finished)
+        self.handle.set_stream(caller)
         return h2d, d2h

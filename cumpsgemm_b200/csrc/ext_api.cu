@@ -197,6 +197,24 @@ int cuMpSGEMM_get_kernel_status(cuMpSGEMM_handle_t h) {
   return v;
 }
 
+int cuMpSGEMM_selftest_bounded_wait(cuMpSGEMM_handle_t h, unsigned limit_ms,
+                                    double *waited_ms) {
+  if (h == nullptr) return -1;
+  DeviceGuard guard(h->device);
+  // the handle's status word doubles as the self-test's status; one DynParams record as scratch
+  unsigned long long *dev_ns = reinterpret_cast<unsigned long long *>(
+      h->dev_dyn_params + (h->dyn_params_length - 1));
+  cudaMemsetAsync(h->dev_status, 0, sizeof(int), h->cuda_stream);
+  if (launch_bounded_wait_selftest(h->dev_status, 1000000ull * limit_ms, dev_ns,
+                                   h->cuda_stream) != cudaSuccess)
+    return -2;
+  unsigned long long ns = 0;
+  cudaMemcpyAsync(&ns, dev_ns, sizeof(ns), cudaMemcpyDeviceToHost, h->cuda_stream);
+  const int status = cuMpSGEMM_get_kernel_status(h); // synchronises and clears
+  if (waited_ms) *waited_ms = static_cast<double>(ns) * 1e-6;
+  return status;
+}
+
 void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t h, size_t bytes) {
   h->workspace_limit_bytes = bytes;
 }

@@ -185,6 +185,9 @@ struct TcecGemmArgs {
   unsigned long long *debug = nullptr; // optional stall breakdown buffer (8 x u64)
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
+// Self-test of the bounded mbarrier wait (see cuMpSGEMM_selftest_bounded_wait).
+cudaError_t launch_bounded_wait_selftest(int *dev_status, unsigned long long limit_ns,
+                                         unsigned long long *dev_waited_ns, cudaStream_t stream);
 // Dynamic shared memory and stage count of a tile configuration (for tests/docs).
 int tcec_gemm_stages(int tile_n, bool error_correction);
 

@@ -80,7 +80,7 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s
 // records `code` in the global status word (first error wins).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int *abort_smem, int *status_gmem,
-                                          int code) {
+                                          int code, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -88,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3f) == 0) {
       if (*abort_smem) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_smem = 1;
         if (status_gmem != nullptr) atomicCAS(status_gmem, 0, code);
         return false;

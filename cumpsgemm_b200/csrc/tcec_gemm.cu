@@ -406,7 +406,36 @@ template <int KIND, bool EC> cudaError_t launch_by_tile(const TcecGemmArgs &a, c
   }
 }
 
+// One CTA waits, with the library's bounded wait, on an mbarrier that nothing ever signals.
+// The wait must give up after limit_ns, record kErrWaitFull in *status and let the kernel
+// return normally: this is the path every GEMM wait takes if a copy or an MMA never completes.
+__global__ void bounded_wait_selftest_kernel(int *status, unsigned long long limit_ns,
+                                             unsigned long long *waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    abort_flag = 0;
+    ptx::mbar_init_fence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0u, &abort_flag, status,
+                                   ptx::kErrWaitFull, limit_ns);
+    *waited_ns = ptx::globaltimer_ns() - t0;
+    if (ok) atomicCAS(status, 0, -1); // a wait on an idle barrier must not succeed
+  }
+  __syncthreads();
+}
+
 } // namespace
+
+cudaError_t launch_bounded_wait_selftest(int *dev_status, unsigned long long limit_ns,
+                                         unsigned long long *dev_waited_ns, cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(dev_status, limit_ns, dev_waited_ns);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream) {
   if (a.kind == SplitKind::fp16) {

@@ -125,6 +125,12 @@ cublasStatus_t cuMpSGEMM_sgemm_module(
  * code in a device word.  This call synchronises the handle's stream, returns the word and
  * clears it.  0 = no error. */
 int cuMpSGEMM_get_kernel_status(cuMpSGEMM_handle_t handle);
+/* Self-test of the bounded wait: a one-CTA kernel waits, with the same routine the GEMM kernels
+ * use, on a barrier that nothing signals; after limit_ms it must give up, record its code and
+ * return normally.  Returns the status word (expected: 2, the "waited for operands" code) and
+ * the time the wait took.  The context stays usable; nothing faults. */
+int cuMpSGEMM_selftest_bounded_wait(cuMpSGEMM_handle_t handle, unsigned limit_ms,
+                                    double *waited_ms);
 /* Cap (bytes) for the operand workspace a strided-batch call may use at once; batches beyond
  * it are processed in chunks.  0 restores the default (8 GiB). */
 void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);

@@ -281,3 +281,38 @@ def test_large_size_against_sampled_fp64(handle, oracle, n):
     truth_gpu = (A @ B + 0.5 * c0.view(n, n).t().double())
     diff = (truth_gpu - c.view(n, n).t().double()).norm() / truth_gpu.norm()
     assert diff.item() < oracle.error_threshold(True, n)
+
+
+def test_host_buffer_gemm_pipelined_matches_resident(handle, oracle):
+    """api.HostGemm (pinned host operands, column-block pipeline) against the resident call."""
+    from cumpsgemm_b200 import api
+
+    torch = _torch()
+    m, n, k = 300, 1000, 260
+    a, b, c0 = oracle.gen_uniform(1, m * k), oracle.gen_uniform(2, k * n), oracle.gen_uniform(3, m * n)
+    ah, bh = torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory()
+    for blocks in (1, 7):
+        ch = torch.from_numpy(c0.copy()).pin_memory()
+        host = api.HostGemm(handle, column_blocks=blocks)
+        h2d, d2h = host.gemm(N, N, m, n, k, 1.5, ah, m, bh, k, 0.5, ch, m, FP16TCEC)
+        torch.cuda.synchronize()
+        assert (h2d, d2h) == ((m * k + k * n + m * n) * 4, m * n * 4)
+        truth = oracle.gemm_f64(N, N, m, n, k, 1.5, a, m, b, k, 0.5, c0, m)
+        assert oracle.residual(truth, ch.numpy(), m) < oracle.error_threshold(True, k)
+    handle.use_current_torch_stream()
+
+
+def test_bounded_wait_gives_up_cleanly(handle, oracle):
+    """Failure detection without a fault: a wait on a barrier nothing signals runs out after
+    its limit, the status word carries the code, and the context keeps working."""
+    torch = _torch()
+    status, waited = handle.selftest_bounded_wait(200)
+    assert status == 2                      # "MMA issuer waited for operands"
+    assert 200.0 <= waited < 1000.0
+    assert handle.kernel_status() == 0      # cleared by the read
+    m = n = k = 128
+    a, b = _dev(oracle.gen_uniform(1, m * k)), _dev(oracle.gen_uniform(2, k * n))
+    c = torch.zeros(m * n, device="cuda")
+    handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, FP16TCEC)
+    truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a.cpu().numpy(), m, b.cpu().numpy(), k, 0.0, None, m)
+    assert oracle.residual(truth, c.cpu().numpy(), m) < oracle.error_threshold(True, k)
