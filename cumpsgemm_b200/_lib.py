@@ -99,7 +99,10 @@ PROTOTYPES = {
     "cuMpSGEMM_hijack_enable_restoring_AB_after_scaling": (None, []),
     "cuMpSGEMM_hijack_disable_restoring_AB_after_scaling": (None, []),
     "cuMpSGEMM_hijack_get_last_called_function_str": (C.c_size_t, [C.c_char_p, C.c_size_t]),
+    "cuMpSGEMM_hijack_set_last_called_function_str": (None, [C.c_char_p]),
     "cuMpSGEMM_hijack_clear_last_called_function_str": (None, []),
+    "cuMpSGEMM_hijack_enable_custom_gemm_Mx2x2": (None, []),
+    "cuMpSGEMM_hijack_disable_custom_gemm_Mx2x2": (None, []),
     "cuMpSGEMM_hijack_is_library_loaded": (i32, []),
     "cuMpSGEMM_hijack_set_control_function": (None, [vp]),
     "cuMpSGEMM_get_compute_mode_internal": (i32, [C.c_char_p, vp, i32, i32, u32, u32, u32]),
@@ -121,6 +124,23 @@ PROTOTYPES = {
                                         vp, i32, C.c_longlong, vp, vp, i32, C.c_longlong, i32]),
     "cublasGemmEx": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i32, i32, vp, vp,
                            i32, i32, i32, i32]),
+    "cublasSgemm_v2_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 + [vp, vp, C.c_int64, vp, C.c_int64,
+                                                              vp, vp, C.c_int64]),
+    "cublasCgemm_v2_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 + [vp, vp, C.c_int64, vp, C.c_int64,
+                                                              vp, vp, C.c_int64]),
+    "cublasSgemmStridedBatched_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 +
+                                     [vp, vp, C.c_int64, C.c_longlong, vp, C.c_int64, C.c_longlong,
+                                      vp, vp, C.c_int64, C.c_longlong, C.c_int64]),
+    "cublasCgemmStridedBatched_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 +
+                                     [vp, vp, C.c_int64, C.c_longlong, vp, C.c_int64, C.c_longlong,
+                                      vp, vp, C.c_int64, C.c_longlong, C.c_int64]),
+    "cublasGemmEx_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 +
+                        [vp, vp, i32, C.c_int64, vp, i32, C.c_int64, vp, vp, i32, C.c_int64, i32,
+                         i32]),
+    "cublasGemmStridedBatchedEx_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 +
+                                      [vp, vp, i32, C.c_int64, C.c_longlong, vp, i32, C.c_int64,
+                                       C.c_longlong, vp, vp, i32, C.c_int64, C.c_longlong,
+                                       C.c_int64, i32, i32]),
     "cublasGemmStridedBatchedEx": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, i32,
                                          C.c_longlong, vp, i32, i32, C.c_longlong, vp, vp, i32,
                                          i32, C.c_longlong, i32, i32, i32]),

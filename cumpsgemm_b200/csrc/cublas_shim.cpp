@@ -317,36 +317,39 @@ cublasStatus_t hijack_core(const char *func_name, cublasHandle_t cublas_handle,
     }
     CallTimer timer(stream, timer_name<T>(func_name, op_A, op_B, m, n, k, batched ? batch : 0));
     cublasStatus_t res;
+    // The 64-bit entry points of the real cuBLAS take every size this layer accepts.
     if (!batched) {
-      using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int,
-                                      int, int, const void *, const void *, cudaDataType, int,
-                                      const void *, cudaDataType, int, const void *, void *,
-                                      cudaDataType, int, cublasComputeType_t, cublasGemmAlgo_t);
-      static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmEx"));
+      using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int64_t,
+                                      int64_t, int64_t, const void *, const void *, cudaDataType,
+                                      int64_t, const void *, cudaDataType, int64_t, const void *,
+                                      void *, cudaDataType, int64_t, cublasComputeType_t,
+                                      cublasGemmAlgo_t);
+      static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmEx_64"));
       if (fn == nullptr) {
         log_error(std::string("Could not load the cuBLAS function \"") + func_name + "\"");
         return CUBLAS_STATUS_NOT_INITIALIZED;
       }
-      res = fn(cublas_handle, op_A, op_B, static_cast<int>(m), static_cast<int>(n),
-               static_cast<int>(k), alpha, a, cuda_type<T>(), static_cast<int>(lda), b,
-               cuda_type<T>(), static_cast<int>(ldb), beta, c, cuda_type<T>(),
-               static_cast<int>(ldc), compute_type, algo);
+      res = fn(cublas_handle, op_A, op_B, static_cast<int64_t>(m), static_cast<int64_t>(n),
+               static_cast<int64_t>(k), alpha, a, cuda_type<T>(), static_cast<int64_t>(lda), b,
+               cuda_type<T>(), static_cast<int64_t>(ldb), beta, c, cuda_type<T>(),
+               static_cast<int64_t>(ldc), compute_type, algo);
     } else {
-      using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int,
-                                      int, int, const void *, const void *, cudaDataType, int,
-                                      long long int, const void *, cudaDataType, int,
-                                      long long int, const void *, void *, cudaDataType, int,
-                                      long long int, int, cublasComputeType_t, cublasGemmAlgo_t);
-      static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmStridedBatchedEx"));
+      using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int64_t,
+                                      int64_t, int64_t, const void *, const void *, cudaDataType,
+                                      int64_t, long long int, const void *, cudaDataType, int64_t,
+                                      long long int, const void *, void *, cudaDataType, int64_t,
+                                      long long int, int64_t, cublasComputeType_t,
+                                      cublasGemmAlgo_t);
+      static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmStridedBatchedEx_64"));
       if (fn == nullptr) {
         log_error(std::string("Could not load the cuBLAS function \"") + func_name + "\"");
         return CUBLAS_STATUS_NOT_INITIALIZED;
       }
-      res = fn(cublas_handle, op_A, op_B, static_cast<int>(m), static_cast<int>(n),
-               static_cast<int>(k), alpha, a, cuda_type<T>(), static_cast<int>(lda),
-               static_cast<long long>(stridea), b, cuda_type<T>(), static_cast<int>(ldb),
-               static_cast<long long>(strideb), beta, c, cuda_type<T>(), static_cast<int>(ldc),
-               static_cast<long long>(stridec), static_cast<int>(batch), compute_type, algo);
+      res = fn(cublas_handle, op_A, op_B, static_cast<int64_t>(m), static_cast<int64_t>(n),
+               static_cast<int64_t>(k), alpha, a, cuda_type<T>(), static_cast<int64_t>(lda),
+               static_cast<long long>(stridea), b, cuda_type<T>(), static_cast<int64_t>(ldb),
+               static_cast<long long>(strideb), beta, c, cuda_type<T>(), static_cast<int64_t>(ldc),
+               static_cast<long long>(stridec), static_cast<int64_t>(batch), compute_type, algo);
     }
     if (h->exp_stats.enabled) {
       // statistics of the result, as the reference records for pass-through calls
@@ -519,6 +522,124 @@ cublasStatus_t cublasGemmStridedBatchedEx(
   return fn(handle, transa, transb, m, n, k, alpha, A, Atype, lda, strideA, B, Btype, ldb, strideB,
             beta, C, Ctype, ldc, strideC, batchCount, computeType, algo);
 }
+
+// ---- 64-bit integer interface of cuBLAS 12 (cublas_api.h: cublasSgemm_v2_64, ...).  The
+//      reference does not intercept these; applications built with CUBLAS_64 reach them.
+#define CUMPSGEMM_NEG6(a, b, c, d, e, f) ((a) < 0 || (b) < 0 || (c) < 0 || (d) < 0 || (e) < 0 || (f) < 0)
+
+cublasStatus_t cublasSgemm_v2_64(cublasHandle_t handle, cublasOperation_t transa,
+                                 cublasOperation_t transb, int64_t m, int64_t n, int64_t k,
+                                 const float *alpha, const float *A, int64_t lda, const float *B,
+                                 int64_t ldb, const float *beta, float *C, int64_t ldc) {
+  if (CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc)) return CUBLAS_STATUS_INVALID_VALUE;
+  return hijack_core<float>(__func__, handle, transa, transb, m, n, k, alpha, A, lda, 0, B, ldb, 0,
+                            beta, C, ldc, 0, 0, false);
+}
+
+cublasStatus_t cublasCgemm_v2_64(cublasHandle_t handle, cublasOperation_t transa,
+                                 cublasOperation_t transb, int64_t m, int64_t n, int64_t k,
+                                 const cuComplex *alpha, const cuComplex *A, int64_t lda,
+                                 const cuComplex *B, int64_t ldb, const cuComplex *beta,
+                                 cuComplex *C, int64_t ldc) {
+  if (CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc)) return CUBLAS_STATUS_INVALID_VALUE;
+  return hijack_core<cuComplex>(__func__, handle, transa, transb, m, n, k, alpha, A, lda, 0, B,
+                                ldb, 0, beta, C, ldc, 0, 0, false);
+}
+
+cublasStatus_t cublasSgemmStridedBatched_64(cublasHandle_t handle, cublasOperation_t transa,
+                                            cublasOperation_t transb, int64_t m, int64_t n,
+                                            int64_t k, const float *alpha, const float *A,
+                                            int64_t lda, long long int strideA, const float *B,
+                                            int64_t ldb, long long int strideB, const float *beta,
+                                            float *C, int64_t ldc, long long int strideC,
+                                            int64_t batchCount) {
+  if (CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc) || batchCount < 0 || strideA < 0 || strideB < 0 ||
+      strideC < 0)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  return hijack_core<float>(__func__, handle, transa, transb, m, n, k, alpha, A, lda, strideA, B,
+                            ldb, strideB, beta, C, ldc, strideC, batchCount, true);
+}
+
+cublasStatus_t cublasCgemmStridedBatched_64(cublasHandle_t handle, cublasOperation_t transa,
+                                            cublasOperation_t transb, int64_t m, int64_t n,
+                                            int64_t k, const cuComplex *alpha, const cuComplex *A,
+                                            int64_t lda, long long int strideA, const cuComplex *B,
+                                            int64_t ldb, long long int strideB,
+                                            const cuComplex *beta, cuComplex *C, int64_t ldc,
+                                            long long int strideC, int64_t batchCount) {
+  if (CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc) || batchCount < 0 || strideA < 0 || strideB < 0 ||
+      strideC < 0)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  return hijack_core<cuComplex>(__func__, handle, transa, transb, m, n, k, alpha, A, lda, strideA,
+                                B, ldb, strideB, beta, C, ldc, strideC, batchCount, true);
+}
+
+cublasStatus_t cublasGemmEx_64(cublasHandle_t handle, cublasOperation_t transa,
+                               cublasOperation_t transb, int64_t m, int64_t n, int64_t k,
+                               const void *alpha, const void *A, cudaDataType_t Atype, int64_t lda,
+                               const void *B, cudaDataType_t Btype, int64_t ldb, const void *beta,
+                               void *C, cudaDataType_t Ctype, int64_t ldc,
+                               cublasComputeType_t computeType, cublasGemmAlgo_t algo) {
+  if (!CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc)) {
+    if (Atype == CUDA_R_32F && Btype == CUDA_R_32F && Ctype == CUDA_R_32F) {
+      return hijack_core<float>(__func__, handle, transa, transb, m, n, k,
+                                static_cast<const float *>(alpha), static_cast<const float *>(A),
+                                lda, 0, static_cast<const float *>(B), ldb, 0,
+                                static_cast<const float *>(beta), static_cast<float *>(C), ldc, 0,
+                                0, false);
+    }
+    if (Atype == CUDA_C_32F && Btype == CUDA_C_32F && Ctype == CUDA_C_32F) {
+      return hijack_core<cuComplex>(
+          __func__, handle, transa, transb, m, n, k, static_cast<const cuComplex *>(alpha),
+          static_cast<const cuComplex *>(A), lda, 0, static_cast<const cuComplex *>(B), ldb, 0,
+          static_cast<const cuComplex *>(beta), static_cast<cuComplex *>(C), ldc, 0, 0, false);
+    }
+  }
+  using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int64_t,
+                                  int64_t, int64_t, const void *, const void *, cudaDataType_t,
+                                  int64_t, const void *, cudaDataType_t, int64_t, const void *,
+                                  void *, cudaDataType_t, int64_t, cublasComputeType_t,
+                                  cublasGemmAlgo_t);
+  static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmEx_64"));
+  if (fn == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  return fn(handle, transa, transb, m, n, k, alpha, A, Atype, lda, B, Btype, ldb, beta, C, Ctype,
+            ldc, computeType, algo);
+}
+
+cublasStatus_t cublasGemmStridedBatchedEx_64(
+    cublasHandle_t handle, cublasOperation_t transa, cublasOperation_t transb, int64_t m,
+    int64_t n, int64_t k, const void *alpha, const void *A, cudaDataType_t Atype, int64_t lda,
+    long long int strideA, const void *B, cudaDataType_t Btype, int64_t ldb, long long int strideB,
+    const void *beta, void *C, cudaDataType_t Ctype, int64_t ldc, long long int strideC,
+    int64_t batchCount, cublasComputeType_t computeType, cublasGemmAlgo_t algo) {
+  if (!CUMPSGEMM_NEG6(m, n, k, lda, ldb, ldc) && batchCount >= 0 && strideA >= 0 &&
+      strideB >= 0 && strideC >= 0) {
+    if (Atype == CUDA_R_32F && Btype == CUDA_R_32F && Ctype == CUDA_R_32F) {
+      return hijack_core<float>(__func__, handle, transa, transb, m, n, k,
+                                static_cast<const float *>(alpha), static_cast<const float *>(A),
+                                lda, strideA, static_cast<const float *>(B), ldb, strideB,
+                                static_cast<const float *>(beta), static_cast<float *>(C), ldc,
+                                strideC, batchCount, true);
+    }
+    if (Atype == CUDA_C_32F && Btype == CUDA_C_32F && Ctype == CUDA_C_32F) {
+      return hijack_core<cuComplex>(
+          __func__, handle, transa, transb, m, n, k, static_cast<const cuComplex *>(alpha),
+          static_cast<const cuComplex *>(A), lda, strideA, static_cast<const cuComplex *>(B), ldb,
+          strideB, static_cast<const cuComplex *>(beta), static_cast<cuComplex *>(C), ldc, strideC,
+          batchCount, true);
+    }
+  }
+  using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int64_t,
+                                  int64_t, int64_t, const void *, const void *, cudaDataType_t,
+                                  int64_t, long long int, const void *, cudaDataType_t, int64_t,
+                                  long long int, const void *, void *, cudaDataType_t, int64_t,
+                                  long long int, int64_t, cublasComputeType_t, cublasGemmAlgo_t);
+  static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmStridedBatchedEx_64"));
+  if (fn == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  return fn(handle, transa, transb, m, n, k, alpha, A, Atype, lda, strideA, B, Btype, ldb, strideB,
+            beta, C, Ctype, ldc, strideC, batchCount, computeType, algo);
+}
+#undef CUMPSGEMM_NEG6
 
 } // extern "C"
 

@@ -283,6 +283,15 @@ size_t cuMpSGEMM_hijack_get_last_called_function_str(char *buf, size_t size) {
   }
   return s.size();
 }
+void cuMpSGEMM_hijack_set_last_called_function_str(const char *str) {
+  cumpsgemm::hijack_control::set_last_called_function_str(str != nullptr ? str : "");
+}
+void cuMpSGEMM_hijack_enable_custom_gemm_Mx2x2(void) {
+  cumpsgemm::hijack_control::enable_custom_gemm_Mx2x2();
+}
+void cuMpSGEMM_hijack_disable_custom_gemm_Mx2x2(void) {
+  cumpsgemm::hijack_control::disable_custom_gemm_Mx2x2();
+}
 void cuMpSGEMM_hijack_clear_last_called_function_str(void) {
   cumpsgemm::hijack_control::clear_last_called_function_str();
 }

@@ -53,6 +53,14 @@ template <> struct Scalar<cuComplex> {
   static float im(const cuComplex *p) { return p->y; }
 };
 
+// Tile width for a problem (CUMPSGEMM_TILE_N overrides).  256 means the CTA-pair kernel's
+// 256 x 256 tile when the mode is error-corrected.  Measured on B200 (GEMM kernel only, us):
+//   m=n=k   BN=64   BN=128   pairs
+//   1024     22.1    24.8     34.0      (16 pair tiles)
+//   2048    116      71.0     59.4      (64 pair tiles on 74 pair slots)
+//   4096    805     407      335
+// so the wide tile wins from about two thirds of a wave upwards; narrower tiles move the same
+// operand bytes for fewer MMAs and only pay off when they are needed to occupy the GPU.
 int pick_tile_n(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
                 std::uint64_t batch) {
   const char *force = std::getenv("CUMPSGEMM_TILE_N");
@@ -60,11 +68,10 @@ int pick_tile_n(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
     const int v = std::atoi(force);
     if (v == 256 || v == 128 || v == 64) return v;
   }
-  const std::uint64_t tiles_m = (m_exp + 127) / 128;
-  for (int bn : {256, 128}) {
-    const std::uint64_t tiles = tiles_m * ((n + bn - 1) / bn) * batch;
-    if (tiles >= h->num_sms) return bn;
-  }
+  const std::uint64_t pair_tiles = ((m_exp + 255) / 256) * ((n + 255) / 256) * batch;
+  if (3 * pair_tiles >= h->num_sms) return 256; // >= 2/3 of the num_sms/2 pair slots
+  const std::uint64_t tiles_128 = ((m_exp + 127) / 128) * ((n + 127) / 128) * batch;
+  if (tiles_128 >= h->num_sms) return 128;
   return 64;
 }
 

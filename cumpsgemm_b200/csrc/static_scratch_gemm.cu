@@ -23,7 +23,7 @@
 //     uses, padding included, so nothing stale is ever read and nothing needs clearing; but
 //     two calls that overlap in time on the same GPU (different streams, different threads)
 //     race on it.  Serialise them on one stream.
-#include "internal.hpp"
+#include "gemm_common.cuh"
 
 #include <cumpsgemm/cumpsgemm_ext.h>
 #include <mutex>
@@ -73,10 +73,10 @@ int pick_tile(int num_sms, std::uint64_t m, std::uint64_t n) {
     const int v = std::atoi(force);
     if (v == 256 || v == 128 || v == 64) return v;
   }
-  const std::uint64_t tiles_m = (m + 127) / 128;
-  for (int bn : {256, 128}) {
-    if (tiles_m * ((n + bn - 1) / bn) >= static_cast<std::uint64_t>(num_sms)) return bn;
-  }
+  const std::uint64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  if (3 * pair_tiles >= static_cast<std::uint64_t>(num_sms)) return 256;
+  const std::uint64_t tiles_128 = ((m + 127) / 128) * ((n + 127) / 128);
+  if (tiles_128 >= static_cast<std::uint64_t>(num_sms)) return 128;
   return 64;
 }
 
@@ -114,7 +114,9 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
   const SplitKind kind = (compute_mode == CUMPSGEMM_FP16TCEC) ? SplitKind::fp16 : SplitKind::tf32;
   const std::size_t es = (kind == SplitKind::fp16) ? 2 : 4;
   const int tile_n = pick_tile(pd->num_sms, m, n);
-  const std::uint64_t rows_pad_a = round_up(m, 128);
+  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
+  const bool use_pair = tile_n == 256 && !(pair_env != nullptr && pair_env[0] == '0');
+  const std::uint64_t rows_pad_a = round_up(m, use_pair ? 256 : 128);
   const std::uint64_t rows_pad_b = round_up(n, tile_n);
   const std::uint64_t k_pad = round_up(k, 64);
   const std::uint64_t bytes_a = 2 * rows_pad_a * k_pad * es;
@@ -182,7 +184,7 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
     g.dyn = nullptr;
     g.tile_n = tile_n;
     g.dev_status = nullptr; // no handle, hence no status word; waits stay bounded
-    err = launch_tcec_gemm(g, stream);
+    err = use_pair ? launch_tcec_gemm_pair(g, stream) : launch_tcec_gemm(g, stream);
   }
   if (err != cudaSuccess) {
     log_error(std::string("cuMpSGEMM_sgemm_static_scratch: launch failed: ") +

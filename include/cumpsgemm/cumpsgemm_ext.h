@@ -161,7 +161,10 @@ void cuMpSGEMM_hijack_enable_restoring_AB_after_scaling(void);
 void cuMpSGEMM_hijack_disable_restoring_AB_after_scaling(void);
 /* copies at most size-1 characters and NUL-terminates; returns the full length */
 size_t cuMpSGEMM_hijack_get_last_called_function_str(char *buf, size_t size);
+void cuMpSGEMM_hijack_set_last_called_function_str(const char *str);
 void cuMpSGEMM_hijack_clear_last_called_function_str(void);
+void cuMpSGEMM_hijack_enable_custom_gemm_Mx2x2(void);
+void cuMpSGEMM_hijack_disable_custom_gemm_Mx2x2(void);
 int cuMpSGEMM_hijack_is_library_loaded(void);
 /* C callback form of hijack_control::set_control_function; NULL unsets. */
 typedef int (*cuMpSGEMM_control_function_c_t)(int op_A, int op_B, unsigned m, unsigned n,

@@ -28,7 +28,9 @@ def test_every_declared_symbol_is_exported(clib):
     missing = [n for n in sorted(declared) if not hasattr(clib, n)]
     assert not missing, missing
     for n in ("cublasSgemm_v2", "cublasCgemm_v2", "cublasSgemmStridedBatched",
-              "cublasCgemmStridedBatched", "cublasGemmEx", "cublasGemmStridedBatchedEx"):
+              "cublasCgemmStridedBatched", "cublasGemmEx", "cublasGemmStridedBatchedEx",
+              "cublasSgemm_v2_64", "cublasCgemm_v2_64", "cublasSgemmStridedBatched_64",
+              "cublasCgemmStridedBatched_64", "cublasGemmEx_64", "cublasGemmStridedBatchedEx_64"):
         assert hasattr(clib, n), n
 
 

@@ -175,3 +175,35 @@ def test_auto_mode_log_line_under_ld_preload(client):
 def test_client_without_preload_is_plain_cublas(client):
     res, st, out = _run_client(client, ["s", 1100, 1060, 1030], False, {"CUMPSGEMM_INFO": "1"})
     assert st == 0 and "[cuMpSGEMM LOG]" not in out
+
+
+def test_64bit_entry_points(oracle):
+    """cuBLAS 12's 64-bit integer interface (cublasSgemm_v2_64, ...) is intercepted as well, and
+    the pass-through modes forward to the real cublasGemmEx_64."""
+    torch, lib = _setup()
+    blas = torch.cuda.current_blas_handle()
+    m, n, k = 260, 300, 200
+    a, b = oracle.gen_uniform(1, m * k), oracle.gen_uniform(2, k * n)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    truth = oracle.gemm_f64(0, 0, m, n, k, 1.0, a, m, b, k, 0.0, None, m)
+    alpha, beta = C.c_float(1.0), C.c_float(0.0)
+    try:
+        for mode, thr in ((1, oracle.error_threshold(True, k)), (5, 1e-5)):
+            lib.cuMpSGEMM_hijack_set_compute_mode(mode)
+            dc = torch.zeros(m * n, device="cuda")
+            assert lib.cublasSgemm_v2_64(blas, 0, 0, m, n, k, C.byref(alpha), da.data_ptr(), m,
+                                         db.data_ptr(), k, C.byref(beta), dc.data_ptr(), m) == 0
+            torch.cuda.synchronize()
+            assert oracle.residual(truth, dc.cpu().numpy(), m) < thr
+            buf = C.create_string_buffer(128)
+            lib.cuMpSGEMM_hijack_get_last_called_function_str(buf, 128)
+            assert buf.value.decode().startswith(f"cublasSgemm_v2_64,N,N,{m},{n},{k},1,")
+        lib.cuMpSGEMM_hijack_set_compute_mode(2)
+        dc = torch.zeros(m * n, device="cuda")
+        assert lib.cublasGemmEx_64(blas, 0, 0, m, n, k, C.byref(alpha), da.data_ptr(), 0, m,
+                                   db.data_ptr(), 0, k, C.byref(beta), dc.data_ptr(), 0, m, 68,
+                                   -1) == 0
+        torch.cuda.synchronize()
+        assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    finally:
+        lib.cuMpSGEMM_hijack_unset_compute_mode()
