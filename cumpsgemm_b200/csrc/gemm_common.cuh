@@ -27,6 +27,9 @@ struct GemmKernelParams {
   unsigned long long *debug;
   // Stages whose hi*hi products accumulate in TMEM before one drain (pair kernel; 1 or 2).
   uint32_t drain_chunk;
+  // Pair tiles in the whole launch (tiles_m * tiles_n * batch); the persistent pair kernel
+  // walks them with a stride of the number of clusters in the grid.
+  uint32_t total_tiles;
 };
 
 // Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {128 bytes of K, box_rows, 1},

@@ -69,7 +69,8 @@ enum : int {
   kErrWaitD0Empty = 3, // MMA issuer waited for the drain of the main accumulator
   kErrWaitD0Full = 4,  // epilogue waited for a chunk's main accumulator
   kErrWaitD1Full = 5,  // epilogue waited for the correction accumulator
-  kErrBadLaunch = 6
+  kErrBadLaunch = 6,
+  kErrWaitD1Empty = 7  // MMA issuer waited for the epilogue to read the correction accumulator
 };
 
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s

@@ -1,20 +1,27 @@
-// Error-corrected tensor-core GEMM, CTA-pair variant (tcgen05 cta_group::2).
+// Error-corrected tensor-core GEMM, persistent CTA-pair variant (tcgen05 cta_group::2).
 //
 // Same arithmetic, panels and barrier protocol as tcec_gemm.cu (which replaces the
-// reference's src/cumpsgemm_kernel.cuh:468-585); what changes is the tile.  A cluster of two
-// CTAs owns a 256 x 256 tile of C: each CTA loads its own 128 rows of A (hi, lo) and its own
-// 128-row half of the B tile (hi, lo), the even CTA issues every tcgen05.mma for the pair,
-// and each CTA's TMEM receives its own 128 x 256 part of the accumulators, which its own
-// epilogue warps drain.  Per SM and k-stage this moves 64 KiB from L2 instead of 96 KiB and
-// leaves room for three stages instead of two.
+// reference's src/cumpsgemm_kernel.cuh:468-585); what changes is the tile and the schedule.
+// A cluster of two CTAs owns 256 x 256 tiles of C: each CTA loads its own 128 rows of A
+// (hi, lo) and its own 128-row half of the B tile (hi, lo), the even CTA issues every
+// tcgen05.mma for the pair, and each CTA's TMEM receives its own 128 x 256 part of the
+// accumulators, which its own epilogue warps drain.  Per SM and k-stage this moves 64 KiB from
+// L2 instead of 96 KiB and leaves room for three stages instead of two.
+//
+// The kernel is persistent: the grid holds at most one cluster per SM pair and every cluster
+// walks the tiles  t = cluster, cluster + #clusters, ...  The producer and the MMA issuer run
+// ahead into the next tile while the epilogue warps still write the previous one: the next
+// tile's operands are loaded and its hi*hi products start as soon as the last drain of D0 is
+// done; its correction products wait only until the epilogue has copied D1 into registers.
 //
 // Barriers (one set per CTA at identical shared-memory offsets; "leader" = cluster rank 0):
 //   full[s]   leader's only: 1 arrival (leader's producer, expect_tx of both CTAs' bytes);
 //             both CTAs' TMA loads complete on it (cta_group::2 loads, no multicast)
 //   empty[s]  in both CTAs: 1 arrival, tcgen05.commit multicast from the leader
-//   d0_full   in both CTAs: commit multicast after the hi*hi products of a stage
+//   d0_full   in both CTAs: commit multicast after the hi*hi products of a chunk of stages
 //   d0_empty  leader's only: 16 arrivals = 8 drain warps of each CTA (remote mbarrier arrive)
-//   d1_full   in both CTAs: commit multicast after the last stage
+//   d1_full   in both CTAs: commit multicast after the last stage of a tile
+//   d1_empty  leader's only: 16 arrivals, after the epilogue warps have read D1
 // Every wait is bounded; no TMA multicast is used.
 #include "gemm_common.cuh"
 #include "ptx.cuh"
@@ -29,8 +36,8 @@ constexpr int NUM_THREADS = 384;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t D1_COL = 256;
-constexpr int TILE_BYTES = 128 * ROW_BYTES;       // every sub-tile is 128 rows
-constexpr int STAGE_BYTES = 4 * TILE_BYTES;       // A_hi, A_lo, B_hi, B_lo
+constexpr int TILE_BYTES = 128 * ROW_BYTES; // every sub-tile is 128 rows
+constexpr int STAGE_BYTES = 4 * TILE_BYTES; // A_hi, A_lo, B_hi, B_lo
 constexpr int STAGES = 3;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
@@ -42,6 +49,32 @@ __device__ __forceinline__ void mma_pair(uint32_t d, uint64_t a, uint64_t b, uin
   } else {
     ptx::mma_tf32_ss_pair(d, a, b, idesc, acc);
   }
+}
+
+struct TileCoord {
+  uint32_t batch;
+  int m0; // first row of this CTA's 128 rows
+  int n0; // first column of the pair's 256 columns
+};
+
+// Grouped raster over pair tiles: tiles that run at the same time share A and B panels in L2.
+__device__ __forceinline__ TileCoord tile_coord(uint32_t tile, const GemmKernelParams &p,
+                                                uint32_t rank) {
+  constexpr uint32_t GROUP_M = 8;
+  const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
+  TileCoord c;
+  c.batch = tile / tiles_per_batch;
+  const uint32_t t = tile - c.batch * tiles_per_batch;
+  const uint32_t tiles_in_group = GROUP_M * p.tiles_n;
+  const uint32_t group_id = t / tiles_in_group;
+  const uint32_t first_m = group_id * GROUP_M;
+  const uint32_t group_rows = min(p.tiles_m - first_m, GROUP_M);
+  const uint32_t in_group = t - group_id * tiles_in_group;
+  const uint32_t tile_m = first_m + in_group % group_rows;
+  const uint32_t tile_n = in_group / group_rows;
+  c.m0 = static_cast<int>(tile_m * 2 * BM_CTA + rank * BM_CTA);
+  c.n0 = static_cast<int>(tile_n * BN_PAIR);
+  return c;
 }
 
 template <int KIND>
@@ -66,30 +99,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   uint64_t *d0_full = bars + 2 * STAGES;
   uint64_t *d0_empty = bars + 2 * STAGES + 1;
   uint64_t *d1_full = bars + 2 * STAGES + 2;
-  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 3);
+  uint64_t *d1_empty = bars + 2 * STAGES + 3;
+  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
   const bool leader = (rank == 0);
-
-  // ---- pair-tile coordinates, grouped raster over pairs
-  const uint32_t pair = blockIdx.x >> 1;
-  const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
-  const uint32_t batch_id = pair / tiles_per_batch;
-  const uint32_t t = pair - batch_id * tiles_per_batch;
-  constexpr uint32_t GROUP_M = 8;
-  const uint32_t tiles_in_group = GROUP_M * p.tiles_n;
-  const uint32_t group_id = t / tiles_in_group;
-  const uint32_t first_m = group_id * GROUP_M;
-  const uint32_t group_rows = min(p.tiles_m - first_m, GROUP_M);
-  const uint32_t in_group = t - group_id * tiles_in_group;
-  const uint32_t tile_m = first_m + in_group % group_rows;
-  const uint32_t tile_n = in_group / group_rows;
-  const int m0 = static_cast<int>(tile_m * 2 * BM_CTA + rank * BM_CTA); // this CTA's rows
-  const int n0 = static_cast<int>(tile_n * BN_PAIR);                    // the pair's columns
-  const int nb0 = n0 + static_cast<int>(rank) * 128;                    // this CTA's B rows
+  const uint32_t cluster_id = blockIdx.x >> 1;
+  const uint32_t num_clusters = gridDim.x >> 1;
+  const uint32_t total_tiles = p.total_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -99,6 +119,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     ptx::mbar_init(ptx::smem_u32(d0_full), 1);
     ptx::mbar_init(ptx::smem_u32(d0_empty), 2 * NUM_EPI_WARPS);
     ptx::mbar_init(ptx::smem_u32(d1_full), 1);
+    ptx::mbar_init(ptx::smem_u32(d1_empty), 2 * NUM_EPI_WARPS);
     *abort_flag = 0;
     ptx::mbar_init_fence();
     ptx::prefetch_tensormap(&map_a);
@@ -122,22 +143,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   if (warp == 0) {
     // ================================================================ TMA producer (both CTAs)
     if (lane == 0) {
-      const int za = static_cast<int>(batch_id * 2u);
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        const uint32_t s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1u;
-        if (!ptx::mbar_wait_timed(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
-                                  ptx::kErrWaitEmpty, dbg, &dbg_wait))
-          break;
-        const uint32_t fb_local = ptx::smem_u32(&full_bar[s]);
-        if (leader) ptx::mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES);
-        const uint32_t fb = ptx::map_to_cta(fb_local, 0); // the leader's barrier
-        const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
-        const int kc = static_cast<int>(kb * BK);
-        ptx::tma_load_3d_pair(st, &map_a, fb, kc, m0, za);
-        ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, kc, m0, za + 1);
-        ptx::tma_load_3d_pair(st + 2 * TILE_BYTES, &map_b, fb, kc, nb0, za);
-        ptx::tma_load_3d_pair(st + 3 * TILE_BYTES, &map_b, fb, kc, nb0, za + 1);
+      uint32_t it = 0; // stage uses since kernel start, across tiles
+      bool ok = true;
+      for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+        const TileCoord tc = tile_coord(tile, p, rank);
+        const int za = static_cast<int>(tc.batch * 2u);
+        const int nb0 = tc.n0 + static_cast<int>(rank) * 128; // this CTA's rows of the B tile
+        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = ptx::mbar_wait_timed(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
+                                    ptx::kErrWaitEmpty, dbg, &dbg_wait);
+          if (!ok) break;
+          const uint32_t fb_local = ptx::smem_u32(&full_bar[s]);
+          if (leader) ptx::mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES);
+          const uint32_t fb = ptx::map_to_cta(fb_local, 0); // the leader's barrier
+          const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
+          const int kc = static_cast<int>(kb * BK);
+          ptx::tma_load_3d_pair(st, &map_a, fb, kc, tc.m0, za);
+          ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, kc, tc.m0, za + 1);
+          ptx::tma_load_3d_pair(st + 2 * TILE_BYTES, &map_b, fb, kc, nb0, za);
+          ptx::tma_load_3d_pair(st + 3 * TILE_BYTES, &map_b, fb, kc, nb0, za + 1);
+        }
       }
       if (dbg) atomicAdd(p.debug + 2, dbg_wait);
     }
@@ -150,46 +177,57 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       const long long dbg_t0 = clock64();
       const uint32_t chunk = p.drain_chunk;
-      uint32_t chunk_idx = 0, in_chunk = 0;
-      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
-        const uint32_t s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1u;
-        ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
-                                  ptx::kErrWaitFull, dbg, &dbg_wait);
-        if (!ok) break;
-        if (in_chunk == 0) {
-          // D0 of the previous chunk must have been drained before it is overwritten.
-          ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (chunk_idx & 1u) ^ 1u, abort_flag,
-                                    p.status, ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
+      uint32_t it = 0, chunk_idx = 0, tile_iter = 0;
+      for (uint32_t tile = cluster_id; tile < total_tiles && ok;
+           tile += num_clusters, ++tile_iter) {
+        uint32_t in_chunk = 0;
+        for (uint32_t kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
+                                    ptx::kErrWaitFull, dbg, &dbg_wait);
           if (!ok) break;
+          if (in_chunk == 0) {
+            // D0 of the previous chunk must have been drained before it is overwritten.
+            ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (chunk_idx & 1u) ^ 1u, abort_flag,
+                                      p.status, ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
+            if (!ok) break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t a_hi = ptx::make_kmajor_desc<ROW_BYTES>(st);
+          const uint64_t a_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + TILE_BYTES);
+          const uint64_t b_hi = ptx::make_kmajor_desc<ROW_BYTES>(st + 2 * TILE_BYTES);
+          const uint64_t b_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + 3 * TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < K_STEPS; ++ks)
+            mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
+                           (in_chunk > 0 || ks > 0) ? 1u : 0u);
+          const bool last_in_chunk = (in_chunk + 1 == chunk) || (kb + 1 == k_blocks);
+          if (last_in_chunk) ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
+          if (kb == 0) {
+            // D1 still holds the previous tile's corrections until its epilogue has read them.
+            ok = ptx::mbar_wait_timed(ptx::smem_u32(d1_empty), (tile_iter & 1u) ^ 1u, abort_flag,
+                                      p.status, ptx::kErrWaitD1Empty, dbg, &dbg_wait2);
+            if (!ok) break;
+            ptx::tc_fence_after();
+          }
+#pragma unroll
+          for (int ks = 0; ks < K_STEPS; ++ks)
+            mma_pair<KIND>(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+          for (int ks = 0; ks < K_STEPS; ++ks)
+            mma_pair<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
+          ptx::tc_commit_pair(ptx::smem_u32(&empty_bar[s]), BOTH);
+          if (last_in_chunk) {
+            in_chunk = 0;
+            ++chunk_idx;
+          } else {
+            ++in_chunk;
+          }
         }
-        ptx::tc_fence_after();
-        const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t a_hi = ptx::make_kmajor_desc<ROW_BYTES>(st);
-        const uint64_t a_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + TILE_BYTES);
-        const uint64_t b_hi = ptx::make_kmajor_desc<ROW_BYTES>(st + 2 * TILE_BYTES);
-        const uint64_t b_lo = ptx::make_kmajor_desc<ROW_BYTES>(st + 3 * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < K_STEPS; ++ks)
-          mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
-                         (in_chunk > 0 || ks > 0) ? 1u : 0u);
-        const bool last_in_chunk = (in_chunk + 1 == chunk) || (kb + 1 == k_blocks);
-        if (last_in_chunk) ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
-#pragma unroll
-        for (int ks = 0; ks < K_STEPS; ++ks)
-          mma_pair<KIND>(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < K_STEPS; ++ks)
-          mma_pair<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
-        ptx::tc_commit_pair(ptx::smem_u32(&empty_bar[s]), BOTH);
-        if (last_in_chunk) {
-          in_chunk = 0;
-          ++chunk_idx;
-        } else {
-          ++in_chunk;
-        }
+        if (ok) ptx::tc_commit_pair(ptx::smem_u32(d1_full), BOTH);
       }
-      if (ok) ptx::tc_commit_pair(ptx::smem_u32(d1_full), BOTH);
       if (dbg) {
         atomicAdd(p.debug + 0, dbg_wait);
         atomicAdd(p.debug + 1, dbg_wait2);
@@ -204,62 +242,70 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const uint32_t col_base = half * CPT;
     const uint32_t d0_empty_leader = ptx::map_to_cta(ptx::smem_u32(d0_empty), 0);
-
-    float acc[CPT];
-#pragma unroll
-    for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
-
-    bool ok = true;
+    const uint32_t d1_empty_leader = ptx::map_to_cta(ptx::smem_u32(d1_empty), 0);
     const uint32_t n_chunks = (k_blocks + p.drain_chunk - 1) / p.drain_chunk;
-    for (uint32_t kb = 0; kb < n_chunks; ++kb) { // kb counts drains here
-      ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), kb & 1u, abort_flag, p.status,
-                                ptx::kErrWaitD0Full, dbg, &dbg_wait);
+    const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
+    const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
+    const float br = p.beta_r, bi = p.beta_i;
+    const bool read_c = (br != 0.f) || (bi != 0.f);
+    const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
+    const float lsi = p.lo_scale_inv;
+
+    uint32_t chunk_idx = 0, tile_iter = 0;
+    bool ok = true;
+    for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++tile_iter) {
+      const TileCoord tc = tile_coord(tile, p, rank);
+      float acc[CPT];
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
+
+      for (uint32_t c = 0; c < n_chunks; ++c, ++chunk_idx) {
+        ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), chunk_idx & 1u, abort_flag, p.status,
+                                  ptx::kErrWaitD0Full, dbg, &dbg_wait);
+        if (!ok) break;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int pc = 0; pc < CPT / 32; ++pc) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + col_base + pc * 32, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[pc * 32 + i] += __uint_as_float(v[i]);
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(d0_empty_leader);
+      }
+      if (!ok) break;
+
+      ok = ptx::mbar_wait(ptx::smem_u32(d1_full), tile_iter & 1u, abort_flag, p.status,
+                          ptx::kErrWaitD1Full);
       if (!ok) break;
       ptx::tc_fence_after();
 #pragma unroll
       for (int pc = 0; pc < CPT / 32; ++pc) {
         uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(tmem_base + lane_addr + col_base + pc * 32, v);
+        ptx::tmem_ld_32x32b_x32(tmem_base + D1_COL + lane_addr + col_base + pc * 32, v);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[pc * 32 + i] += __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i)
+          acc[pc * 32 + i] = fmaf(__uint_as_float(v[i]), lsi, acc[pc * 32 + i]);
       }
+      // D1 is in registers: the issuer may start the next tile's correction products
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive_cluster(d0_empty_leader);
-    }
+      if (lane == 0) ptx::mbar_arrive_cluster(d1_empty_leader);
 
-    if (dbg && warp == 4 && lane == 0) atomicAdd(p.debug + 3, dbg_wait);
-    if (ok) {
-      ok = ptx::mbar_wait(ptx::smem_u32(d1_full), 0u, abort_flag, p.status, ptx::kErrWaitD1Full);
-      if (ok) {
-        ptx::tc_fence_after();
-        const float lsi = p.lo_scale_inv;
-#pragma unroll
-        for (int pc = 0; pc < CPT / 32; ++pc) {
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(tmem_base + D1_COL + lane_addr + col_base + pc * 32, v);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            acc[pc * 32 + i] = fmaf(__uint_as_float(v[i]), lsi, acc[pc * 32 + i]);
-        }
-      }
-    }
-
-    if (ok) {
-      const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
-      const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
-      const float br = p.beta_r, bi = p.beta_i;
-      const bool read_c = (br != 0.f) || (bi != 0.f);
-      const uint32_t row = static_cast<uint32_t>(m0) + quarter * 32u + static_cast<uint32_t>(lane);
+      // C(row, col) = alpha * acc + beta * C(row, col); lanes hold consecutive rows of the
+      // column-major C, so each warp store covers 128 contiguous bytes.
+      const uint32_t row =
+          static_cast<uint32_t>(tc.m0) + quarter * 32u + static_cast<uint32_t>(lane);
       const bool row_ok = row < p.m;
-      float *cbase = p.c + static_cast<uint64_t>(batch_id) * p.stride_c + row;
-      const float sgn = (lane & 1) ? 1.f : -1.f;
+      float *cbase = p.c + static_cast<uint64_t>(tc.batch) * p.stride_c + row;
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
-        const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i);
-        if (col < p.n) {
+        const uint32_t col = static_cast<uint32_t>(tc.n0) + col_base + static_cast<uint32_t>(i);
+        if (col < p.n) { // uniform over the warp
           float *cp = cbase + static_cast<uint64_t>(col) * p.ldc;
           float old = 0.f;
           if (read_c && row_ok) old = *cp;
@@ -277,12 +323,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
         }
       }
     }
+    if (dbg && warp == 4 && lane == 0) atomicAdd(p.debug + 3, dbg_wait);
   }
 
   // ---------------------------------------------------------------- teardown
-  // The peer's shared memory and TMEM are in use by the leader's MMAs until d1_full has fired
-  // in both CTAs; the cluster barrier below keeps either CTA from leaving before the other
-  // has finished its epilogue.
+  // The peer's shared memory and TMEM are in use by the leader's MMAs until the last d1_full
+  // has fired in both CTAs; the cluster barrier below keeps either CTA from leaving before
+  // the other has finished its last epilogue.
   ptx::tc_fence_before();
   __syncthreads();
   ptx::cluster_arrive();
@@ -301,12 +348,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
   auto kernel = tcec_gemm_pair_kernel<KIND>;
   static bool attr_set[64] = {};
+  static int max_clusters[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!attr_set[dev]) {
     cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // one cluster per SM pair; if the device can co-schedule fewer, use what it reports
+    int clusters = sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    int active = 0;
+    if (cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) == cudaSuccess) {
+      if (active > 0 && active < clusters) clusters = active;
+    } else {
+      cudaGetLastError();
+    }
+    max_clusters[dev] = clusters > 0 ? clusters : 1;
     attr_set[dev] = true;
   }
   const uint32_t planes = a.batch * 2u;
@@ -342,11 +406,14 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     // 8 / 32 / 256 stages per drain (FP32 cuBLAS SGEMM on the same inputs: 2.3e-6).
     p.drain_chunk = (v >= 1) ? static_cast<uint32_t>(v) : 2u;
   }
-  const uint64_t grid = 2ull * p.tiles_m * p.tiles_n * a.batch;
-  if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
+  const uint64_t total = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
+  if (total == 0 || total > 0x7fffffffull) return cudaErrorInvalidValue;
   if (a.rows_pad_a < p.tiles_m * 2 * BM_CTA || a.rows_pad_b < p.tiles_n * BN_PAIR)
     return cudaErrorInvalidValue;
-  kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  p.total_tiles = static_cast<uint32_t>(total);
+  const uint32_t clusters = static_cast<uint32_t>(
+      total < static_cast<uint64_t>(max_clusters[dev]) ? total : max_clusters[dev]);
+  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
 
