@@ -457,7 +457,46 @@ def run_sweep(args):
                                                  zc, s, s * s, batch, api.ComputeMode[mode]), 20)
         emit(config=f"cgemm strided batch {mode} batch={batch} m=n=k={s}", ms=ms,
              tflops=8.0 * batch * s ** 3 / ms / 1e9)
-    # config 5a, one GPU's share at 8 GPUs: batch 8 of 8192^3, AUTO decided per call
+    del za, zb, zc
+    if args.sweep_large:
+        # config 5a, one GPU's share at 8 GPUs: batch 8 of 8192^3, N(0,1), AUTO
+        n, batch = 8192, 8
+        a = torch.randn(batch * n * n, device=dev, generator=g)
+        b = torch.randn(batch * n * n, device=dev, generator=g)
+        c = torch.zeros(batch * n * n, device=dev)
+        ms = timeit(lambda: h.gemm_strided_batch(0, 0, n, n, n, 1.0, a, n, n * n, b, n, n * n,
+                                                 0.0, c, n, n * n, batch,
+                                                 api.ComputeMode.FP16TCEC), 3)
+        emit(config=f"sgemm strided batch FP16TCEC batch={batch} m=n=k={n} N(0,1)", ms=ms,
+             tflops=2.0 * batch * n ** 3 / ms / 1e9)
+
+        def auto_call():
+            ia = h.exp_stats_ext(n, n, a, n, batch, n * n)
+            ib = h.exp_stats_ext(n, n, b, n, batch, n * n)
+            h.gemm_strided_batch_with_stats(0, 0, n, n, n, 1.0, a, n, n * n, b, n, n * n, 0.0, c, n,
+                                            n * n, batch, api.ComputeMode.AUTO, ia, ib)
+        ms = timeit(auto_call, 3)
+        emit(config=f"sgemm strided batch AUTO batch={batch} m=n=k={n} N(0,1) (statistics + GEMM)",
+             ms=ms, tflops=2.0 * batch * n ** 3 / ms / 1e9)
+        del a, b, c
+        # config 5b on one GPU: m=n=65536, k=8192, N(0,1)
+        m, k = 65536, 8192
+        a = torch.randn(m * k, device=dev, generator=g)
+        b = torch.randn(k * m, device=dev, generator=g)
+        c = torch.zeros(m * m, device=dev)
+        ms = timeit(lambda: h.gemm(0, 0, m, m, k, 1.0, a, m, b, k, 0.0, c, m,
+                                   api.ComputeMode.FP16TCEC), 2)
+        # spot check of three rows against FP64 on the GPU
+        A = a.view(k, m).t()
+        B = b.view(m, k).t()
+        worst = 0.0
+        for i in (0, 40000, m - 1):
+            truth = A[i].double() @ B.double()
+            got = c.view(m, m)[:, i].double()
+            worst = max(worst, ((truth - got).norm() / truth.norm()).item())
+        emit(config=f"sgemm FP16TCEC m=n={m} k={k} N(0,1), one GPU", ms=ms,
+             tflops=2.0 * m * m * k / ms / 1e9, worst_row_residual=worst)
+        del a, b, c
     status = h.kernel_status()
     emit(config="kernel status after sweep", status=status)
     h.destroy()
@@ -474,6 +513,8 @@ def main():
     ap.add_argument("--beta", type=float, default=0.5)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep-large", action="store_true",
+                    help="with --sweep: also the 8 x 8192^3 batch and the 65536 x 65536 x 8192 GEMM")
     ap.add_argument("--sweep", action="store_true",
                     help="run the other benchmark configurations (documentation runs)")
     args = ap.parse_args()

@@ -124,6 +124,10 @@ PROTOTYPES = {
                                         vp, i32, C.c_longlong, vp, vp, i32, C.c_longlong, i32]),
     "cublasGemmEx": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i32, i32, vp, vp,
                            i32, i32, i32, i32]),
+    "cublasSgemmBatched": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32]),
+    "cublasCgemmBatched": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32, i32]),
+    "cublasGemmBatchedEx": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, i32, vp, i32, i32, vp,
+                                  vp, i32, i32, i32, i32, i32]),
     "cublasSgemm_v2_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 + [vp, vp, C.c_int64, vp, C.c_int64,
                                                               vp, vp, C.c_int64]),
     "cublasCgemm_v2_64": (i32, [vp, i32, i32] + [C.c_int64] * 3 + [vp, vp, C.c_int64, vp, C.c_int64,

@@ -385,6 +385,74 @@ cublasStatus_t hijack_core(const char *func_name, cublasHandle_t cublas_handle,
                           &beta_h, c, ldc, stridec, nb, mode, nullptr, nullptr);
 }
 
+// Pointer-array batches (cublas{S,C}gemmBatched, cublasGemmBatchedEx with FP32 types).  The
+// reference does not intercept these.  FP16TCEC / TF32TCEC (and the non-corrected modes) run on
+// the cuMpSGEMM kernels; every other mode, including AUTO and FP16TCEC_SCALING whose statistics
+// kernels take strided batches only, is forwarded to the real cublasGemmBatchedEx.
+template <class T>
+cublasStatus_t hijack_batched_core(const char *func_name, cublasHandle_t cublas_handle,
+                                   cublasOperation_t op_A, cublasOperation_t op_B, int m, int n,
+                                   int k, const T *alpha, const T *const *a_array, int lda,
+                                   const T *const *b_array, int ldb, const T *beta,
+                                   T *const *c_array, int ldc, int batch) {
+  if (m <= 0 || n <= 0 || k <= 0 || lda <= 0 || ldb <= 0 || ldc <= 0 || batch <= 0)
+    return CUBLAS_STATUS_INVALID_VALUE;
+  cuMpSGEMM_handle_t h = global_handle();
+  if (h == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  const cudaStream_t stream = stream_of(cublas_handle);
+  const cuMpSGEMM_compute_mode_t mode = cuMpSGEMM_get_compute_mode_internal(
+      func_name, cublas_handle, op_A, op_B, static_cast<unsigned>(m), static_cast<unsigned>(n),
+      static_cast<unsigned>(k));
+  const bool dynamic = (g_hijack_mode == HijackMode::dynamic_mode);
+  log_info(std::string(func_name) + " op=(" + op_str(op_A) + ", " + op_str(op_B) + "), shape=(" +
+           std::to_string(m) + ", " + std::to_string(n) + ", " + std::to_string(k) +
+           "), batch=" + std::to_string(batch) +
+           ", mode=" + cuMpSGEMM_get_compute_mode_string(mode) + "[" +
+           (dynamic ? "dynamic" : "static") + "][exp_stats:" + (h->exp_stats.enabled ? "1" : "0") +
+           "]");
+  cumpsgemm::hijack_control::set_last_called_function_str(
+      std::string(func_name) + "," + op_str(op_A) + "," + op_str(op_B) + "," + std::to_string(m) +
+      "," + std::to_string(n) + "," + std::to_string(k) + "," + std::to_string(batch) + "," +
+      cuMpSGEMM_get_compute_mode_string(mode));
+  if (mode == CUMPSGEMM_DRY_RUN) return CUBLAS_STATUS_SUCCESS;
+
+  const bool own_kernels = (mode == CUMPSGEMM_FP16TCEC || mode == CUMPSGEMM_TF32TCEC ||
+                            mode == CUMPSGEMM_FP16TC || mode == CUMPSGEMM_TF32TC);
+  if (!own_kernels) {
+    cublasGemmAlgo_t algo = CUBLAS_GEMM_DEFAULT;
+    cublasComputeType_t compute_type = CUBLAS_COMPUTE_32F;
+    if (mode == CUMPSGEMM_CUBLAS_TF32TC) {
+      algo = CUBLAS_GEMM_DEFAULT_TENSOR_OP;
+      compute_type = CUBLAS_COMPUTE_32F_FAST_TF32;
+    } else if (mode == CUMPSGEMM_CUBLAS_FP16TC) {
+      algo = CUBLAS_GEMM_DEFAULT_TENSOR_OP;
+      compute_type = CUBLAS_COMPUTE_32F_FAST_16F;
+    }
+    using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int,
+                                    int, const void *, const void *const[], cudaDataType, int,
+                                    const void *const[], cudaDataType, int, const void *,
+                                    void *const[], cudaDataType, int, int, cublasComputeType_t,
+                                    cublasGemmAlgo_t);
+    static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmBatchedEx"));
+    if (fn == nullptr) {
+      log_error(std::string("Could not load the cuBLAS function \"") + func_name + "\"");
+      return CUBLAS_STATUS_NOT_INITIALIZED;
+    }
+    return fn(cublas_handle, op_A, op_B, m, n, k, alpha,
+              reinterpret_cast<const void *const *>(a_array), cuda_type<T>(), lda,
+              reinterpret_cast<const void *const *>(b_array), cuda_type<T>(), ldb, beta,
+              reinterpret_cast<void *const *>(c_array), cuda_type<T>(), ldc, batch, compute_type,
+              algo);
+  }
+  T alpha_h, beta_h;
+  if (!fetch_scalars<T>(cublas_handle, stream, alpha, beta, &alpha_h, &beta_h))
+    return CUBLAS_STATUS_INVALID_VALUE;
+  cuMpSGEMM_set_stream(h, stream);
+  return gemm_dispatch<T>(h, op_A, op_B, m, n, k, &alpha_h, nullptr, lda, 0, nullptr, ldb, 0,
+                          &beta_h, nullptr, ldc, 0, batch, mode, nullptr, nullptr, a_array, b_array,
+                          c_array);
+}
+
 } // namespace
 
 // ---------------------------------------------------------------- mode selection
@@ -521,6 +589,59 @@ cublasStatus_t cublasGemmStridedBatchedEx(
                   timer_name<float>(__func__, transa, transb, m, n, k, batchCount));
   return fn(handle, transa, transb, m, n, k, alpha, A, Atype, lda, strideA, B, Btype, ldb, strideB,
             beta, C, Ctype, ldc, strideC, batchCount, computeType, algo);
+}
+
+// ---- pointer-array batches
+cublasStatus_t cublasSgemmBatched(cublasHandle_t handle, cublasOperation_t transa,
+                                  cublasOperation_t transb, int m, int n, int k,
+                                  const float *alpha, const float *const Aarray[], int lda,
+                                  const float *const Barray[], int ldb, const float *beta,
+                                  float *const Carray[], int ldc, int batchCount) {
+  return hijack_batched_core<float>(__func__, handle, transa, transb, m, n, k, alpha, Aarray, lda,
+                                    Barray, ldb, beta, Carray, ldc, batchCount);
+}
+
+cublasStatus_t cublasCgemmBatched(cublasHandle_t handle, cublasOperation_t transa,
+                                  cublasOperation_t transb, int m, int n, int k,
+                                  const cuComplex *alpha, const cuComplex *const Aarray[], int lda,
+                                  const cuComplex *const Barray[], int ldb, const cuComplex *beta,
+                                  cuComplex *const Carray[], int ldc, int batchCount) {
+  return hijack_batched_core<cuComplex>(__func__, handle, transa, transb, m, n, k, alpha, Aarray,
+                                        lda, Barray, ldb, beta, Carray, ldc, batchCount);
+}
+
+cublasStatus_t cublasGemmBatchedEx(cublasHandle_t handle, cublasOperation_t transa,
+                                   cublasOperation_t transb, int m, int n, int k,
+                                   const void *alpha, const void *const Aarray[],
+                                   cudaDataType_t Atype, int lda, const void *const Barray[],
+                                   cudaDataType_t Btype, int ldb, const void *beta,
+                                   void *const Carray[], cudaDataType_t Ctype, int ldc,
+                                   int batchCount, cublasComputeType_t computeType,
+                                   cublasGemmAlgo_t algo) {
+  if (Atype == CUDA_R_32F && Btype == CUDA_R_32F && Ctype == CUDA_R_32F) {
+    return hijack_batched_core<float>(
+        __func__, handle, transa, transb, m, n, k, static_cast<const float *>(alpha),
+        reinterpret_cast<const float *const *>(Aarray), lda,
+        reinterpret_cast<const float *const *>(Barray), ldb, static_cast<const float *>(beta),
+        reinterpret_cast<float *const *>(Carray), ldc, batchCount);
+  }
+  if (Atype == CUDA_C_32F && Btype == CUDA_C_32F && Ctype == CUDA_C_32F) {
+    return hijack_batched_core<cuComplex>(
+        __func__, handle, transa, transb, m, n, k, static_cast<const cuComplex *>(alpha),
+        reinterpret_cast<const cuComplex *const *>(Aarray), lda,
+        reinterpret_cast<const cuComplex *const *>(Barray), ldb,
+        static_cast<const cuComplex *>(beta), reinterpret_cast<cuComplex *const *>(Carray), ldc,
+        batchCount);
+  }
+  using fn_t = cublasStatus_t (*)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int,
+                                  int, const void *, const void *const[], cudaDataType_t, int,
+                                  const void *const[], cudaDataType_t, int, const void *,
+                                  void *const[], cudaDataType_t, int, int, cublasComputeType_t,
+                                  cublasGemmAlgo_t);
+  static fn_t fn = reinterpret_cast<fn_t>(real_cublas_symbol("cublasGemmBatchedEx"));
+  if (fn == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  return fn(handle, transa, transb, m, n, k, alpha, Aarray, Atype, lda, Barray, Btype, ldb, beta,
+            Carray, Ctype, ldc, batchCount, computeType, algo);
 }
 
 // ---- 64-bit integer interface of cuBLAS 12 (cublas_api.h: cublasSgemm_v2_64, ...).  The

@@ -84,16 +84,20 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
                              std::uint64_t ldb, std::uint64_t strideb, const T *beta, T *c,
                              std::uint64_t ldc, std::uint64_t stridec, std::uint64_t batch,
                              cuMpSGEMM_compute_mode_t mode, const DynParams *dyn,
-                             unsigned *used_kernel_module_id) {
+                             unsigned *used_kernel_module_id, const T *const *a_array,
+                             const T *const *b_array, T *const *c_array) {
   constexpr bool is_complex = std::is_same<T, cuComplex>::value;
   if (h == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
   if (mode == CUMPSGEMM_DRY_RUN) return CUBLAS_STATUS_SUCCESS;
+  const bool ptr_arrays = (a_array != nullptr) || (b_array != nullptr) || (c_array != nullptr);
+  if (ptr_arrays && (a_array == nullptr || b_array == nullptr || c_array == nullptr))
+    return CUBLAS_STATUS_INVALID_VALUE;
   if (m == 0 || n == 0 || k == 0 || batch == 0 || alpha == nullptr || beta == nullptr ||
-      a == nullptr || b == nullptr || c == nullptr)
+      (!ptr_arrays && (a == nullptr || b == nullptr || c == nullptr)))
     return CUBLAS_STATUS_INVALID_VALUE;
   const bool a_n = (op_A == CUBLAS_OP_N), b_n = (op_B == CUBLAS_OP_N);
   if (lda < (a_n ? m : k) || ldb < (b_n ? k : n) || ldc < m) return CUBLAS_STATUS_INVALID_VALUE;
-  if (m > 0x3fffffffull || n > 0x7fffffffull || k > 0x3fffffffull || batch > 65535ull)
+  if (m > 0x3fffffffull || n > 0x7fffffffull || k > 0x3fffffffull || batch > 0x3fffffffull)
     return CUBLAS_STATUS_INVALID_VALUE;
 
   bool want_fp16 = false, want_tf32 = false, ec = true;
@@ -154,6 +158,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       h->workspace_limit_bytes ? h->workspace_limit_bytes : kDefaultWorkspaceLimit;
   std::uint64_t chunk = std::max<std::uint64_t>(1, limit / (bytes_a_1 + bytes_b_1));
   chunk = std::min<std::uint64_t>(chunk, batch);
+  chunk = std::min<std::uint64_t>(chunk, 32768); // planes of a tensor map, tiles of a launch
   if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1))) {
     log_error("failed to allocate the operand workspace");
     return CUBLAS_STATUS_ALLOC_FAILED;
@@ -178,7 +183,8 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       sa.src_k_contig = !a_n;
       sa.rows = m;
       sa.k = k;
-      sa.src = a + b0 * stridea;
+      sa.src = ptr_arrays ? nullptr : a + b0 * stridea;
+      sa.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(a_array + b0) : nullptr;
       sa.ld = lda;
       sa.stride = stridea;
       sa.batch = nb;
@@ -192,19 +198,18 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
         for (auto &e : tt.e) cudaEventCreate(&e);
         cudaEventRecord(tt.e[0], h->cuda_stream);
       }
-      err = launch_split(sa, h->cuda_stream);
-      if (err != cudaSuccess) break;
       SplitArgs sb = sa;
       sb.operand = Operand::B;
       sb.conjugate = is_complex && op_B == CUBLAS_OP_C;
       sb.src_k_contig = b_n;
       sb.rows = n;
-      sb.src = b + b0 * strideb;
+      sb.src = ptr_arrays ? nullptr : b + b0 * strideb;
+      sb.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(b_array + b0) : nullptr;
       sb.ld = ldb;
       sb.stride = strideb;
       sb.panel = ws_b;
       sb.rows_pad = rows_pad_b;
-      err = launch_split(sb, h->cuda_stream);
+      err = launch_split_pair(sa, sb, h->cuda_stream);
       if (err != cudaSuccess) break;
       if (h->kernel_timing) cudaEventRecord(tt.e[1], h->cuda_stream);
 
@@ -219,7 +224,8 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       g.batch = nb;
       g.panel_a = ws_a;
       g.panel_b = ws_b;
-      g.c = reinterpret_cast<float *>(c + b0 * stridec);
+      g.c = ptr_arrays ? nullptr : reinterpret_cast<float *>(c + b0 * stridec);
+      g.c_array = ptr_arrays ? reinterpret_cast<float *const *>(c_array + b0) : nullptr;
       g.ldc = ldc * fpe;
       g.stride_c = stridec * fpe;
       g.alpha_r = Scalar<T>::re(alpha);
@@ -305,7 +311,8 @@ cublasStatus_t gemm_with_statistics(cuMpSGEMM_handle *h, cublasOperation_t op_A,
       cuMpSGEMM_handle *, cublasOperation_t, cublasOperation_t, std::uint64_t, std::uint64_t,     \
       std::uint64_t, const T *, const T *, std::uint64_t, std::uint64_t, const T *, std::uint64_t, \
       std::uint64_t, const T *, T *, std::uint64_t, std::uint64_t, std::uint64_t,                 \
-      cuMpSGEMM_compute_mode_t, const DynParams *, unsigned *);                                   \
+      cuMpSGEMM_compute_mode_t, const DynParams *, unsigned *, const T *const *,                  \
+      const T *const *, T *const *);                                                              \
   template cublasStatus_t gemm_with_statistics<T>(                                                \
       cuMpSGEMM_handle *, cublasOperation_t, cublasOperation_t, std::uint64_t, std::uint64_t,     \
       std::uint64_t, const T *, const T *, std::uint64_t, std::uint64_t, const T *, std::uint64_t, \

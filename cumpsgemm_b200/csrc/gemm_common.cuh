@@ -11,6 +11,7 @@ constexpr int kGemmRowBytes = 128; // K extent of one stage in bytes = one 128-b
 // Kernel arguments besides the two tensor maps.
 struct GemmKernelParams {
   float *c;
+  float *const *c_array; // pointer-array batches: C of batch b starts at c_array[b] (or null)
   uint64_t ldc;
   uint64_t stride_c;
   uint32_t m, n;

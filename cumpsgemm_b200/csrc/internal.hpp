@@ -153,6 +153,7 @@ struct SplitArgs {
   std::uint64_t rows;  // logical rows of op(X): m for A, n for B (complex: complex elements)
   std::uint64_t k;     // logical K (complex: complex elements)
   const void *src;
+  const void *const *src_array = nullptr; // device array of per-batch pointers (or null)
   std::uint64_t ld;     // in elements of the source type
   std::uint64_t stride; // batch stride in elements of the source type
   std::uint32_t batch;
@@ -162,7 +163,8 @@ struct SplitArgs {
   bool with_lo;            // also write the lo panel
   const DynParams *dyn;    // nullable: scale factor and gating
 };
-cudaError_t launch_split(const SplitArgs &a, cudaStream_t stream);
+// Splits op(A) and op(B) of one GEMM in a single launch.
+cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream);
 
 // ---------------------------------------------------------------- TCEC GEMM
 struct TcecGemmArgs {
@@ -175,6 +177,7 @@ struct TcecGemmArgs {
   const void *panel_a;
   const void *panel_b;
   float *c;
+  float *const *c_array = nullptr; // device array of per-batch C pointers (or null)
   std::uint64_t ldc;      // in floats
   std::uint64_t stride_c; // in floats
   float alpha_r, alpha_i, beta_r, beta_i;
@@ -231,7 +234,10 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
                              std::uint64_t ldb, std::uint64_t strideb, const T *beta, T *c,
                              std::uint64_t ldc, std::uint64_t stridec, std::uint64_t batch,
                              cuMpSGEMM_compute_mode_t mode, const DynParams *dyn,
-                             unsigned *used_kernel_module_id);
+                             unsigned *used_kernel_module_id, const T *const *a_array = nullptr,
+                             const T *const *b_array = nullptr, T *const *c_array = nullptr);
+// a_array / b_array / c_array (device arrays of `batch` device pointers, all three or none)
+// select pointer-array batches; a, b, c and the strides are then ignored.
 
 // Full AUTO / FP16TCEC_SCALING pipeline (statistics -> flag -> fused GEMM).
 // Does not modify A or B.

@@ -39,6 +39,7 @@ __device__ __forceinline__ float to_tf32(float v) {
 
 struct SplitParams {
   const float *src; // complex sources are addressed as pairs of floats
+  const float *const *src_array; // pointer-array batches: matrix b starts at src_array[b]
   uint64_t ld, stride;
   uint64_t rows, k; // logical source extent (complex elements for complex input)
   void *panel;
@@ -52,7 +53,8 @@ struct SplitParams {
 
 // MODE: 0 = real, 1 = complex A', 2 = complex B'
 template <int KIND, int MODE>
-__global__ void __launch_bounds__(THREADS) split_kernel(const SplitParams p) {
+__device__ __forceinline__ void split_generic_body(const SplitParams &p, const uint3 bid,
+                                                   float (*tile)[TILE + 1]) {
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   float scale = 1.f;
   if (p.dyn != nullptr) {
@@ -64,12 +66,13 @@ __global__ void __launch_bounds__(THREADS) split_kernel(const SplitParams p) {
   constexpr int SR = (MODE == 1) ? TILE / 2 : TILE; // source rows per tile
   constexpr int SK = (MODE == 0) ? TILE : TILE / 2; // source k per tile
   constexpr int ES = (MODE == 0) ? 1 : 2;           // floats per source element
-  __shared__ float tile[TILE][TILE + 1];
 
-  const uint32_t b = blockIdx.z;
-  const uint64_t r0 = static_cast<uint64_t>(blockIdx.y) * SR;
-  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * SK;
-  const float *src = p.src + static_cast<uint64_t>(b) * p.stride * ES;
+  const uint32_t b = bid.z;
+  const uint64_t r0 = static_cast<uint64_t>(bid.y) * SR;
+  const uint64_t k0 = static_cast<uint64_t>(bid.x) * SK;
+  const float *src = (p.src_array != nullptr)
+                         ? p.src_array[b]
+                         : p.src + static_cast<uint64_t>(b) * p.stride * ES;
 
   // ---- phase 1: coalesced read along the source-contiguous dimension
   for (int idx = threadIdx.x; idx < SR * SK; idx += THREADS) {
@@ -103,8 +106,8 @@ __global__ void __launch_bounds__(THREADS) split_kernel(const SplitParams p) {
   __syncthreads();
 
   // ---- phase 2: each thread converts 8 consecutive expanded-K values of one expanded row
-  const uint64_t er0 = static_cast<uint64_t>(blockIdx.y) * TILE; // expanded row origin
-  const uint64_t ek0 = static_cast<uint64_t>(blockIdx.x) * TILE; // expanded K origin
+  const uint64_t er0 = static_cast<uint64_t>(bid.y) * TILE; // expanded row origin
+  const uint64_t ek0 = static_cast<uint64_t>(bid.x) * TILE; // expanded K origin
   const uint64_t plane_elems = static_cast<uint64_t>(p.rows_pad) * p.k_pad;
 #pragma unroll
   for (int it = 0; it < TILE * TILE / (THREADS * 8); ++it) {
@@ -211,17 +214,17 @@ __device__ __forceinline__ float4 load4_guarded(const float *p, uint64_t first, 
 // Source is K-contiguous (element (r, kk) at [kk + r*ld]): no transpose, no shared memory.
 // CTA = 128 rows x 64 k; thread = 4 rows x 8 consecutive k, all eight 16-byte loads first.
 template <int KIND>
-__global__ void __launch_bounds__(THREADS) split_kcontig_kernel(const SplitParams p) {
+__device__ __forceinline__ void split_kcontig_body(const SplitParams &p, const uint3 bid) {
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   float scale = 1.f;
   if (p.dyn != nullptr) {
     if (p.dyn->gemm_mode != MY_MODE) return;
     scale = (p.operand == 0) ? p.dyn->scale_a : p.dyn->scale_b;
   }
-  const uint32_t b = blockIdx.z;
+  const uint32_t b = bid.z;
   const float *src = p.src + static_cast<uint64_t>(b) * p.stride;
-  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * 64 + (threadIdx.x & 7) * 8;
-  const uint64_t r_base = static_cast<uint64_t>(blockIdx.y) * 128 + (threadIdx.x >> 3);
+  const uint64_t k0 = static_cast<uint64_t>(bid.x) * 64 + (threadIdx.x & 7) * 8;
+  const uint64_t r_base = static_cast<uint64_t>(bid.y) * 128 + (threadIdx.x >> 3);
   const uint64_t plane_elems = static_cast<uint64_t>(p.rows_pad) * p.k_pad;
   float4 x[4][2];
 #pragma unroll
@@ -247,18 +250,18 @@ __global__ void __launch_bounds__(THREADS) split_kcontig_kernel(const SplitParam
 // Source is row-contiguous (element (r, kk) at [r + kk*ld]): 64 x 64 transpose through
 // shared memory with 16-byte loads along r.
 template <int KIND>
-__global__ void __launch_bounds__(THREADS) split_rcontig_kernel(const SplitParams p) {
+__device__ __forceinline__ void split_rcontig_body(const SplitParams &p, const uint3 bid,
+                                                   float (*tile)[TILE + 1]) {
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   float scale = 1.f;
   if (p.dyn != nullptr) {
     if (p.dyn->gemm_mode != MY_MODE) return;
     scale = (p.operand == 0) ? p.dyn->scale_a : p.dyn->scale_b;
   }
-  __shared__ float tile[TILE][TILE + 1];
-  const uint32_t b = blockIdx.z;
+  const uint32_t b = bid.z;
   const float *src = p.src + static_cast<uint64_t>(b) * p.stride;
-  const uint64_t r0 = static_cast<uint64_t>(blockIdx.y) * TILE;
-  const uint64_t k0 = static_cast<uint64_t>(blockIdx.x) * TILE;
+  const uint64_t r0 = static_cast<uint64_t>(bid.y) * TILE;
+  const uint64_t k0 = static_cast<uint64_t>(bid.x) * TILE;
   const int r4 = (threadIdx.x & 15) * 4;
   const int kq = threadIdx.x >> 4; // 0..15
   float4 x[4];
@@ -291,9 +294,63 @@ __global__ void __launch_bounds__(THREADS) split_rcontig_kernel(const SplitParam
   }
 }
 
-template <int KIND, int MODE> cudaError_t launch(const SplitArgs &a, cudaStream_t stream) {
+// Which body handles an operand.
+enum SplitPath : int { kPathReal = 0, kPathComplexA = 1, kPathComplexB = 2, kPathKContig = 3, kPathRContig = 4 };
+
+// VEC = false leaves the vectorised bodies out, which keeps the register count of the
+// latency-bound generic bodies low (30 instead of 64: twice the resident blocks).
+template <int KIND, bool VEC>
+__device__ __forceinline__ void split_dispatch(const SplitParams &p, int path, const uint3 bid,
+                                               float (*tile)[TILE + 1]) {
+  if constexpr (!VEC) {
+    if (path == kPathReal) split_generic_body<KIND, 0>(p, bid, tile);
+    else if (path == kPathComplexA) split_generic_body<KIND, 1>(p, bid, tile);
+    else split_generic_body<KIND, 2>(p, bid, tile);
+    return;
+  }
+  switch (path) {
+  case kPathReal:
+    split_generic_body<KIND, 0>(p, bid, tile);
+    break;
+  case kPathComplexA:
+    split_generic_body<KIND, 1>(p, bid, tile);
+    break;
+  case kPathComplexB:
+    split_generic_body<KIND, 2>(p, bid, tile);
+    break;
+  case kPathKContig:
+    split_kcontig_body<KIND>(p, bid);
+    break;
+  default:
+    split_rcontig_body<KIND>(p, bid, tile);
+    break;
+  }
+}
+
+// One launch splits both operands of a GEMM: the first blocks_a blocks work on op(A), the
+// rest on op(B).  Saves a launch (and its gap) per GEMM call, which matters for small problems.
+struct SplitJob {
   SplitParams p;
+  int path;
+  uint32_t gx, gy, gz;
+};
+
+template <int KIND, bool VEC>
+__global__ void __launch_bounds__(THREADS) split_dual_kernel(const SplitJob a, const SplitJob b) {
+  __shared__ float tile[TILE][TILE + 1]; // transposing staging tile shared by all paths
+  const uint32_t blocks_a = a.gx * a.gy * a.gz;
+  uint32_t id = blockIdx.x;
+  const SplitJob &j = (id < blocks_a) ? a : b;
+  if (id >= blocks_a) id -= blocks_a;
+  const uint3 bid = make_uint3(id % j.gx, (id / j.gx) % j.gy, id / (j.gx * j.gy));
+  split_dispatch<KIND, VEC>(j.p, j.path, bid, tile);
+}
+
+bool make_job(const SplitArgs &a, SplitJob *job) {
+  if ((a.rows_pad % TILE) != 0 || (a.k_pad % TILE) != 0) return false;
+  SplitParams &p = job->p;
   p.src = reinterpret_cast<const float *>(a.src);
+  p.src_array = reinterpret_cast<const float *const *>(a.src_array);
   p.ld = a.ld;
   p.stride = a.stride;
   p.rows = a.rows;
@@ -306,48 +363,45 @@ template <int KIND, int MODE> cudaError_t launch(const SplitArgs &a, cudaStream_
   p.operand = static_cast<int>(a.operand);
   p.conj = a.conjugate ? 1 : 0;
   p.src_k_contig = a.src_k_contig ? 1 : 0;
-  const dim3 grid(a.k_pad / TILE, a.rows_pad / TILE, a.batch);
-  if (grid.y > 65535u || grid.z > 65535u) return cudaErrorInvalidValue;
-  if constexpr (MODE == 0) {
+  job->gx = a.k_pad / TILE;
+  job->gy = a.rows_pad / TILE;
+  job->gz = a.batch;
+  if (a.is_complex) {
+    job->path = (a.operand == Operand::A) ? kPathComplexA : kPathComplexB;
+  } else {
     const bool aligned = ((reinterpret_cast<uintptr_t>(a.src) & 15u) == 0) && (a.ld % 4 == 0) &&
                          (a.stride % 4 == 0);
-    if (aligned) {
-      if (a.src_k_contig) {
-        const dim3 g2(a.k_pad / 64, (a.rows_pad + 127) / 128, a.batch);
-        split_kcontig_kernel<KIND><<<g2, THREADS, 0, stream>>>(p);
-      } else {
-        split_rcontig_kernel<KIND><<<grid, THREADS, 0, stream>>>(p);
-      }
-      return cudaGetLastError();
+    if (!aligned || a.src_array != nullptr) { // per-matrix alignment is unknown on the host
+      job->path = kPathReal;
+    } else if (a.src_k_contig) {
+      job->path = kPathKContig;
+      job->gy = (a.rows_pad + 127) / 128;
+    } else {
+      job->path = kPathRContig;
     }
   }
-  split_kernel<KIND, MODE><<<grid, THREADS, 0, stream>>>(p);
-  return cudaGetLastError();
+  return static_cast<uint64_t>(job->gx) * job->gy * job->gz <= 0x3fffffffull;
 }
 
 } // namespace
 
-cudaError_t launch_split(const SplitArgs &a, cudaStream_t stream) {
-  if ((a.rows_pad % TILE) != 0 || (a.k_pad % TILE) != 0) return cudaErrorInvalidValue;
-  const int mode = !a.is_complex ? 0 : (a.operand == Operand::A ? 1 : 2);
+cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream) {
+  if (a.kind != b.kind) return cudaErrorInvalidValue;
+  SplitJob ja, jb;
+  if (!make_job(a, &ja) || !make_job(b, &jb)) return cudaErrorInvalidValue;
+  const uint64_t blocks = static_cast<uint64_t>(ja.gx) * ja.gy * ja.gz +
+                          static_cast<uint64_t>(jb.gx) * jb.gy * jb.gz;
+  if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+  const bool vec = (ja.path >= kPathKContig) || (jb.path >= kPathKContig);
+  const unsigned grid = static_cast<unsigned>(blocks);
   if (a.kind == SplitKind::fp16) {
-    switch (mode) {
-    case 0:
-      return launch<0, 0>(a, stream);
-    case 1:
-      return launch<0, 1>(a, stream);
-    default:
-      return launch<0, 2>(a, stream);
-    }
+    if (vec) split_dual_kernel<0, true><<<grid, THREADS, 0, stream>>>(ja, jb);
+    else split_dual_kernel<0, false><<<grid, THREADS, 0, stream>>>(ja, jb);
+  } else {
+    if (vec) split_dual_kernel<1, true><<<grid, THREADS, 0, stream>>>(ja, jb);
+    else split_dual_kernel<1, false><<<grid, THREADS, 0, stream>>>(ja, jb);
   }
-  switch (mode) {
-  case 0:
-    return launch<1, 0>(a, stream);
-  case 1:
-    return launch<1, 1>(a, stream);
-  default:
-    return launch<1, 2>(a, stream);
-  }
+  return cudaGetLastError();
 }
 
 } // namespace cumpsgemm_b200

@@ -149,8 +149,8 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
   sa.k_pad = static_cast<std::uint32_t>(k_pad);
   sa.with_lo = true;
   sa.dyn = nullptr;
-  cudaError_t err = launch_split(sa, stream);
-  if (err == cudaSuccess) {
+  cudaError_t err;
+  {
     SplitArgs sb = sa;
     sb.operand = Operand::B;
     sb.src_k_contig = b_n;
@@ -159,7 +159,7 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
     sb.ld = ldb;
     sb.panel = panel_b;
     sb.rows_pad = static_cast<std::uint32_t>(rows_pad_b);
-    err = launch_split(sb, stream);
+    err = launch_split_pair(sa, sb, stream);
   }
   if (err == cudaSuccess) {
     TcecGemmArgs g;

@@ -262,7 +262,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const bool read_c = (br != 0.f) || (bi != 0.f);
       const uint32_t row = static_cast<uint32_t>(m0) + quarter * 32u + static_cast<uint32_t>(lane);
       const bool row_ok = row < p.m;
-      float *cbase = p.c + static_cast<uint64_t>(batch_id) * p.stride_c + row;
+      float *cbase = ((p.c_array != nullptr) ? p.c_array[batch_id]
+                                              : p.c + static_cast<uint64_t>(batch_id) * p.stride_c) +
+                     row;
       const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
@@ -369,6 +371,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   }
   KernelParams p;
   p.c = a.c;
+  p.c_array = a.c_array;
   p.ldc = a.ldc;
   p.stride_c = a.stride_c;
   p.m = a.m;

@@ -301,7 +301,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       const uint32_t row =
           static_cast<uint32_t>(tc.m0) + quarter * 32u + static_cast<uint32_t>(lane);
       const bool row_ok = row < p.m;
-      float *cbase = p.c + static_cast<uint64_t>(tc.batch) * p.stride_c + row;
+      float *cbase = ((p.c_array != nullptr) ? p.c_array[tc.batch]
+                                              : p.c + static_cast<uint64_t>(tc.batch) * p.stride_c) +
+                     row;
 #pragma unroll
       for (int i = 0; i < CPT; ++i) {
         const uint32_t col = static_cast<uint32_t>(tc.n0) + col_base + static_cast<uint32_t>(i);
@@ -381,6 +383,7 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   }
   GemmKernelParams p;
   p.c = a.c;
+  p.c_array = a.c_array;
   p.ldc = a.ldc;
   p.stride_c = a.stride_c;
   p.m = a.m;

@@ -29,6 +29,7 @@ def test_every_declared_symbol_is_exported(clib):
     assert not missing, missing
     for n in ("cublasSgemm_v2", "cublasCgemm_v2", "cublasSgemmStridedBatched",
               "cublasCgemmStridedBatched", "cublasGemmEx", "cublasGemmStridedBatchedEx",
+              "cublasSgemmBatched", "cublasCgemmBatched", "cublasGemmBatchedEx",
               "cublasSgemm_v2_64", "cublasCgemm_v2_64", "cublasSgemmStridedBatched_64",
               "cublasCgemmStridedBatched_64", "cublasGemmEx_64", "cublasGemmStridedBatchedEx_64"):
         assert hasattr(clib, n), n

@@ -207,3 +207,70 @@ def test_64bit_entry_points(oracle):
         assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
     finally:
         lib.cuMpSGEMM_hijack_unset_compute_mode()
+
+
+def test_pointer_array_batched_entry_points(oracle):
+    """cublasSgemmBatched / cublasCgemmBatched / cublasGemmBatchedEx (FP32): matrices scattered
+    in memory, addressed through device arrays of pointers."""
+    torch, lib = _setup()
+    blas = torch.cuda.current_blas_handle()
+    batch, m, n, k = 5, 70, 130, 90
+    alpha, beta = C.c_float(2.0), C.c_float(0.5)
+    a = [oracle.gen_uniform(10 + i, m * k) for i in range(batch)]
+    b = [oracle.gen_uniform(20 + i, k * n) for i in range(batch)]
+    c0 = [oracle.gen_uniform(30 + i, m * n) for i in range(batch)]
+    da = [torch.from_numpy(x).cuda() for x in a]
+    db = [torch.from_numpy(x).cuda() for x in b]
+
+    def ptrs(ts):
+        return torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device="cuda")
+
+    try:
+        for mode, thr in ((1, oracle.error_threshold(True, k)), (2, oracle.error_threshold(True, k)),
+                          (5, 1e-5), (9, 1e-5)):
+            lib.cuMpSGEMM_hijack_set_compute_mode(mode)
+            dc = [torch.from_numpy(x.copy()).cuda() for x in c0]
+            pa, pb, pc = ptrs(da), ptrs(db), ptrs(dc)
+            st = lib.cublasSgemmBatched(blas, 0, 0, m, n, k, C.byref(alpha), pa.data_ptr(), m,
+                                        pb.data_ptr(), k, C.byref(beta), pc.data_ptr(), m, batch)
+            assert st == 0
+            torch.cuda.synchronize()
+            for i in range(batch):
+                truth = oracle.gemm_f64(0, 0, m, n, k, 2.0, a[i], m, b[i], k, 0.5, c0[i], m)
+                assert oracle.residual(truth, dc[i].cpu().numpy(), m) < thr, (mode, i)
+        # Ex form, op (T, N), alpha/beta unchanged
+        lib.cuMpSGEMM_hijack_set_compute_mode(1)
+        at = [torch.from_numpy(np.ascontiguousarray(x.reshape((m, k), order="F").T).ravel(order="F").copy()).cuda()
+              for x in a]
+        dc = [torch.from_numpy(x.copy()).cuda() for x in c0]
+        pa, pb, pc = ptrs(at), ptrs(db), ptrs(dc)
+        st = lib.cublasGemmBatchedEx(blas, 1, 0, m, n, k, C.byref(alpha), pa.data_ptr(), 0, k,
+                                     pb.data_ptr(), 0, k, C.byref(beta), pc.data_ptr(), 0, m, batch,
+                                     68, -1)
+        assert st == 0
+        torch.cuda.synchronize()
+        for i in range(batch):
+            truth = oracle.gemm_f64(0, 0, m, n, k, 2.0, a[i], m, b[i], k, 0.5, c0[i], m)
+            assert oracle.residual(truth, dc[i].cpu().numpy(), m) < oracle.error_threshold(True, k)
+        # complex
+        za = [(oracle.gen_uniform(40 + i, m * k) + 1j * oracle.gen_uniform(50 + i, m * k)).astype(np.complex64)
+              for i in range(batch)]
+        zb = [(oracle.gen_uniform(60 + i, k * n) + 1j * oracle.gen_uniform(70 + i, k * n)).astype(np.complex64)
+              for i in range(batch)]
+        dza = [torch.from_numpy(x).cuda() for x in za]
+        dzb = [torch.from_numpy(x).cuda() for x in zb]
+        dzc = [torch.zeros(m * n, dtype=torch.complex64, device="cuda") for _ in range(batch)]
+        calpha, cbeta = (C.c_float * 2)(1.0, -1.0), (C.c_float * 2)(0.0, 0.0)
+        pza, pzb, pzc = ptrs(dza), ptrs(dzb), ptrs(dzc)   # keep the pointer arrays alive
+        st = lib.cublasCgemmBatched(blas, 0, 0, m, n, k, calpha, pza.data_ptr(), m,
+                                    pzb.data_ptr(), k, cbeta, pzc.data_ptr(), m, batch)
+        assert st == 0
+        torch.cuda.synchronize()
+        for i in range(batch):
+            truth = oracle.gemm_f64(0, 0, m, n, k, 1 - 1j, za[i], m, zb[i], k, 0.0, None, m)
+            assert oracle.residual(truth, dzc[i].cpu().numpy(), m) < oracle.error_threshold(True, k)
+        buf = C.create_string_buffer(128)
+        lib.cuMpSGEMM_hijack_get_last_called_function_str(buf, 128)
+        assert buf.value.decode() == f"cublasCgemmBatched,N,N,{m},{n},{k},{batch},FP16TCEC"
+    finally:
+        lib.cuMpSGEMM_hijack_unset_compute_mode()
