@@ -349,7 +349,7 @@ def run_ours(args, rank, local_rank, world):
                 "l2": "inputs (1 GiB per matrix) exceed the 126 MB L2; no explicit flush",
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": 3 * args.steps * (2 if mode == api.ComputeMode.AUTO else 1),
+            "gpu_launches": 2 * args.steps * (2 if mode == api.ComputeMode.AUTO else 1),
             "kernel_status": kstatus, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -13,6 +13,7 @@ literally from the reference sources and are compared bit-exactly.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 
@@ -36,8 +37,10 @@ class _Stats(C.Structure):
 def build(with_ref: bool = False) -> None:
     """Compile liboracle.so (and, when asked and possible, the reference-derived objects)."""
     subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
-    if with_ref and Path("/root/reference/src").exists():
-        subprocess.run(["make", "-C", str(HERE), "ref"], check=True, capture_output=True)
+    ref = Path(os.environ.get("CUMPSGEMM_REFERENCE_TREE", "/root/reference"))
+    if with_ref and (ref / "src").exists():
+        subprocess.run(["make", "-C", str(HERE), "ref", f"REF={ref}"], check=True,
+                       capture_output=True)
 
 
 def lib():

@@ -1,5 +1,6 @@
 """Generates the golden fixtures in this folder from the parts of the reference that compile
-with plain g++ (see oracle/Makefile, target `ref`).  Run where /root/reference exists:
+with plain g++ (see oracle/Makefile, target `ref`).  Run where the reference tree is mounted
+(the REF variable of oracle/Makefile):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
