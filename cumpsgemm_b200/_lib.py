@@ -31,6 +31,7 @@ def _proto(lib, name, restype, argtypes):
 _GEMM_ARGS = [vp, i32, i32, u64, u64, u64, vp, vp, u64, vp, u64, vp, vp, u64, i32]
 _GEMM_SB_ARGS = [vp, i32, i32, u64, u64, u64, vp, vp, u64, u64, vp, u64, u64, vp, vp, u64, u64,
                  u64, i32]
+_TINY_ARGS = [vp, i32, i32, u64, vp, vp, u64, u64, vp, u64, u64, vp, vp, u64, u64, u64]
 _STATS_ARGS = [vp, u32, u32, vp, u32, u32, u32]
 _SCALE_ARGS = [vp, u32, u32, u32, u32, vp, u32, u32, u32]
 _SCALE_C_ARGS = [vp, u32, u32, u32, u32, u32, vp, u32, u32, u32]
@@ -115,6 +116,10 @@ PROTOTYPES = {
     "cuMpSGEMM_sgemm_strided_batch_with_stats": (i32, _GEMM_SB_ARGS + [u32, u32]),
     "cuMpSGEMM_cgemm_strided_batch_with_stats": (i32, _GEMM_SB_ARGS + [u32, u32]),
     "cuMpSGEMM_sgemm_static_scratch": (i32, [vp] + _GEMM_ARGS[1:]),
+    "cuMpSGEMM_sgemm_Mx2x2": (i32, _TINY_ARGS),
+    "cuMpSGEMM_cgemm_Mx2x2": (i32, _TINY_ARGS),
+    "cuMpSGEMM_sgemm_2xNx2": (i32, _TINY_ARGS),
+    "cuMpSGEMM_cgemm_2xNx2": (i32, _TINY_ARGS),
     # intercepted cuBLAS symbols (prototypes of cublas_api.h)
     "cublasSgemm_v2": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32]),
     "cublasCgemm_v2": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, vp, i32]),

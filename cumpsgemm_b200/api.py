@@ -179,6 +179,22 @@ class Handle:
             raise CuMpSGEMMError(st, "cuMpSGEMM_*gemm_strided_batch_with_stats")
         return st
 
+    def gemm_tiny(self, long_is_m: bool, op_A: int, op_B: int, length: int, alpha, A: DevPtr,
+                  lda: int, B: DevPtr, ldb: int, beta, Cmat: DevPtr, ldc: int, stridea: int = 0,
+                  strideb: int = 0, stridec: int = 0, batch_count: int = 1,
+                  complex: Optional[bool] = None, check: bool = True) -> int:
+        """cuMpSGEMM_{s,c}gemm_Mx2x2 (long_is_m) / cuMpSGEMM_{s,c}gemm_2xNx2: plain FP32 GEMM
+        with the two short dimensions equal to 2 and a power-of-two long one."""
+        cplx = _is_complex(A, complex)
+        name = "cuMpSGEMM_%sgemm_%s" % ("c" if cplx else "s", "Mx2x2" if long_is_m else "2xNx2")
+        a, b = _scalar(alpha, cplx), _scalar(beta, cplx)
+        st = getattr(self._lib, name)(self._h, op_A, op_B, length, C.cast(a, C.c_void_p), _ptr(A),
+                                      lda, stridea, _ptr(B), ldb, strideb, C.cast(b, C.c_void_p),
+                                      _ptr(Cmat), ldc, stridec, batch_count)
+        if check and st != CUBLAS_STATUS_SUCCESS:
+            raise CuMpSGEMMError(st, name)
+        return st
+
     def gemm_module(self, op_A, op_B, m, n, k, alpha, A, lda, B, ldb, beta, Cmat, ldc,
                     mode) -> Tuple[int, int]:
         """cumpsgemm::gemm<float> with its used_kernel_module_id out-parameter."""

@@ -36,6 +36,7 @@ CUDA_SOURCES = [
     "gemm_api.cu",
     "ext_api.cu",
     "static_scratch_gemm.cu",
+    "tiny_gemm.cu",
 ]
 CPP_SOURCES = ["cublas_shim.cpp", "default_rule.cpp"]
 

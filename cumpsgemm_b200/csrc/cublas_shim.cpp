@@ -286,6 +286,28 @@ cublasStatus_t hijack_core(const char *func_name, cublasHandle_t cublas_handle,
 
   if (mode == CUMPSGEMM_DRY_RUN) return CUBLAS_STATUS_SUCCESS;
 
+  // Two-by-two inner problems with a power-of-two long side go to the dedicated FP32 kernels
+  // whatever the mode, when switched on (reference: src/cumpsgemm_cublas.cu:269-338, :647-725;
+  // (m, 2, 2) is tested before (2, n, 2), so m == n == 2 takes the first route).
+  if (k == 2 && (g_mx2x2_enabled || env_flag("CUMPSGEMM_CUSTOM_GEMM_MX2X2", false))) {
+    const bool long_m = n == 2 && (m & (m - 1)) == 0;
+    const bool long_n = !long_m && m == 2 && (n & (n - 1)) == 0;
+    if (long_m || long_n) {
+      T alpha_t, beta_t;
+      if (!fetch_scalars<T>(cublas_handle, stream, alpha, beta, &alpha_t, &beta_t))
+        return CUBLAS_STATUS_INVALID_VALUE;
+      cuMpSGEMM_set_stream(h, stream);
+      const std::string tname = std::string(std::is_same<T, float>::value ? "s" : "c") + "gemm_" +
+                                (batched ? "strided_batch_" : "") +
+                                (long_m ? "Mx2x2" : "2xNx2");
+      CallTimer timer(stream,
+                      timer_name<T>(tname.c_str(), op_A, op_B, m, n, k, batched ? batch : 0));
+      log_info(long_m ? " +---> gemm_Mx2x2" : " +---> gemm_2xNx2");
+      return tiny_gemm<T>(h, long_m, op_A, op_B, long_m ? m : n, &alpha_t, a, lda, stridea, b,
+                          ldb, strideb, &beta_t, c, ldc, stridec, batched ? batch : 1);
+    }
+  }
+
   if (mode == CUMPSGEMM_CUBLAS || mode == CUMPSGEMM_CUBLAS_FP16TC ||
       mode == CUMPSGEMM_CUBLAS_TF32TC || mode == CUMPSGEMM_CUBLAS_SIMT) {
     // ---------------------------------------------------------------- pass-through

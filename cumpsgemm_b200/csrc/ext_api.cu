@@ -370,4 +370,42 @@ cublasStatus_t cuMpSGEMM_cgemm_strided_batch_with_stats(
                                             id_b);
 }
 
+// ---- two-by-two inner problems (tiny_gemm.cu) ------------------------------------------------
+cublasStatus_t cuMpSGEMM_sgemm_Mx2x2(cuMpSGEMM_handle_t h, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t m, const float *alpha,
+                                     const float *a, uint64_t lda, uint64_t stridea,
+                                     const float *b, uint64_t ldb, uint64_t strideb,
+                                     const float *beta, float *c, uint64_t ldc, uint64_t stridec,
+                                     uint64_t batch_count) {
+  return cumpsgemm_b200::tiny_gemm<float>(h, true, op_A, op_B, m, alpha, a, lda, stridea, b, ldb,
+                                          strideb, beta, c, ldc, stridec, batch_count);
+}
+cublasStatus_t cuMpSGEMM_cgemm_Mx2x2(cuMpSGEMM_handle_t h, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t m, const cuComplex *alpha,
+                                     const cuComplex *a, uint64_t lda, uint64_t stridea,
+                                     const cuComplex *b, uint64_t ldb, uint64_t strideb,
+                                     const cuComplex *beta, cuComplex *c, uint64_t ldc,
+                                     uint64_t stridec, uint64_t batch_count) {
+  return cumpsgemm_b200::tiny_gemm<cuComplex>(h, true, op_A, op_B, m, alpha, a, lda, stridea, b,
+                                              ldb, strideb, beta, c, ldc, stridec, batch_count);
+}
+cublasStatus_t cuMpSGEMM_sgemm_2xNx2(cuMpSGEMM_handle_t h, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t n, const float *alpha,
+                                     const float *a, uint64_t lda, uint64_t stridea,
+                                     const float *b, uint64_t ldb, uint64_t strideb,
+                                     const float *beta, float *c, uint64_t ldc, uint64_t stridec,
+                                     uint64_t batch_count) {
+  return cumpsgemm_b200::tiny_gemm<float>(h, false, op_A, op_B, n, alpha, a, lda, stridea, b, ldb,
+                                          strideb, beta, c, ldc, stridec, batch_count);
+}
+cublasStatus_t cuMpSGEMM_cgemm_2xNx2(cuMpSGEMM_handle_t h, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t n, const cuComplex *alpha,
+                                     const cuComplex *a, uint64_t lda, uint64_t stridea,
+                                     const cuComplex *b, uint64_t ldb, uint64_t strideb,
+                                     const cuComplex *beta, cuComplex *c, uint64_t ldc,
+                                     uint64_t stridec, uint64_t batch_count) {
+  return cumpsgemm_b200::tiny_gemm<cuComplex>(h, false, op_A, op_B, n, alpha, a, lda, stridea, b,
+                                              ldb, strideb, beta, c, ldc, stridec, batch_count);
+}
+
 } // extern "C"

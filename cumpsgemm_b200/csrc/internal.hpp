@@ -222,6 +222,15 @@ void launch_scaling(cuMpSGEMM_handle *h, ScaleOp op, unsigned m, unsigned n, T *
 DynParams *prepare_dyn_params(cuMpSGEMM_handle *h, unsigned flag_id, unsigned stats_id_a,
                               unsigned stats_id_b);
 
+// FP32 GEMMs whose two short dimensions are 2 (tiny_gemm.cu).  long_is_m: C = op(A)(len x 2)
+// op(B)(2 x 2); otherwise C = op(A)(2 x 2) op(B)(2 x len).  len must be a power of two.
+template <class T>
+cublasStatus_t tiny_gemm(cuMpSGEMM_handle *h, bool long_is_m, cublasOperation_t op_A,
+                         cublasOperation_t op_B, std::uint64_t len, const T *alpha, const T *a,
+                         std::uint64_t lda, std::uint64_t stride_a, const T *b, std::uint64_t ldb,
+                         std::uint64_t stride_b, const T *beta, T *c, std::uint64_t ldc,
+                         std::uint64_t stride_c, std::uint64_t batch);
+
 // ---------------------------------------------------------------- GEMM dispatch
 // Shared implementation behind gemm<T> / gemm_stridedBatch<T>.
 // `dyn` != nullptr selects the fused scaling path (scale in the split pass,

@@ -216,6 +216,42 @@ cublasStatus_t cuMpSGEMM_cgemm_strided_batch_with_stats(
     cuComplex *c, uint64_t ldc, uint64_t stridec, uint64_t batch_count,
     cuMpSGEMM_compute_mode_t mode, unsigned stats_id_a, unsigned stats_id_b);
 
+/* ---- two-by-two inner problems ------------------------------------------- */
+/* C = alpha op(A) op(B) + beta C in plain FP32 for the shapes the reference hands to the
+ * third-party cuGEMM-Mx2x2 kernels (src/cumpsgemm_cublas.cu:269-338, :647-725):
+ *   *_Mx2x2: op(A) is m x 2, op(B) is 2 x 2, C is m x 2;
+ *   *_2xNx2: op(A) is 2 x 2, op(B) is 2 x n, C is 2 x n;
+ * m resp. n a power of two (anything else returns CUBLAS_STATUS_INVALID_VALUE).  Column-major
+ * device pointers, host alpha / beta, leading dimensions and batch strides in elements;
+ * batch_count == 1 with any strides is the single GEMM.  The interception layer takes this
+ * route for such shapes when CUMPSGEMM_CUSTOM_GEMM_MX2X2=1 or after
+ * hijack_control::enable_custom_gemm_Mx2x2(), whatever the compute mode, as the reference
+ * does. */
+cublasStatus_t cuMpSGEMM_sgemm_Mx2x2(cuMpSGEMM_handle_t handle, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t m, const float *alpha,
+                                     const float *a, uint64_t lda, uint64_t stridea,
+                                     const float *b, uint64_t ldb, uint64_t strideb,
+                                     const float *beta, float *c, uint64_t ldc, uint64_t stridec,
+                                     uint64_t batch_count);
+cublasStatus_t cuMpSGEMM_cgemm_Mx2x2(cuMpSGEMM_handle_t handle, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t m, const cuComplex *alpha,
+                                     const cuComplex *a, uint64_t lda, uint64_t stridea,
+                                     const cuComplex *b, uint64_t ldb, uint64_t strideb,
+                                     const cuComplex *beta, cuComplex *c, uint64_t ldc,
+                                     uint64_t stridec, uint64_t batch_count);
+cublasStatus_t cuMpSGEMM_sgemm_2xNx2(cuMpSGEMM_handle_t handle, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t n, const float *alpha,
+                                     const float *a, uint64_t lda, uint64_t stridea,
+                                     const float *b, uint64_t ldb, uint64_t strideb,
+                                     const float *beta, float *c, uint64_t ldc, uint64_t stridec,
+                                     uint64_t batch_count);
+cublasStatus_t cuMpSGEMM_cgemm_2xNx2(cuMpSGEMM_handle_t handle, cublasOperation_t op_A,
+                                     cublasOperation_t op_B, uint64_t n, const cuComplex *alpha,
+                                     const cuComplex *a, uint64_t lda, uint64_t stridea,
+                                     const cuComplex *b, uint64_t ldb, uint64_t strideb,
+                                     const cuComplex *beta, cuComplex *c, uint64_t ldc,
+                                     uint64_t stridec, uint64_t batch_count);
+
 /* ---- allocation-free FP32 GEMM ------------------------------------------- */
 /* No counterpart in the reference.  For callers that may not allocate device memory (a
  * process whose memory budget is fixed at start-up, a loop that cannot take the device

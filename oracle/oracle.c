@@ -453,3 +453,94 @@ void oracle_scale(int what, float *ptr, size_t m, size_t n, size_t ld, size_t ba
     for (size_t j = 0; j < n; ++j)
       for (size_t i = 0; i < m * f; ++i) ptr[b * stride * f + j * ld * f + i] *= coef;
 }
+
+/* ------------------------------------------------------------------ two-by-two inner problems
+ * Plain FP32 restatement of the shapes the reference hands to the third-party cuGEMM-Mx2x2
+ * kernels (src/cumpsgemm_cublas.cu:269-338 single, :647-725 strided batch; that library's
+ * source is not in the reference tree: PARITY UNPINNED at bit level, pinned against the FP64
+ * truth by tolerance).  The operation order is the one the device kernel documents, written
+ * with fmaf() and with contraction switched off so that both sides round identically.
+ * fpe = 1 real, 2 complex (interleaved).  long_is_m: C (len x 2) = op(A)(len x 2) op(B)(2 x 2);
+ * otherwise C (2 x len) = op(A)(2 x 2) op(B)(2 x len).  Leading dimensions and strides in
+ * elements of the matrix type. */
+typedef struct { float re, im; } tiny_c;
+
+__attribute__((optimize("fp-contract=off")))
+static tiny_c tiny_dot2(tiny_c a0, tiny_c b0, tiny_c a1, tiny_c b1, int cplx) {
+  tiny_c p;
+  if (!cplx) {
+    p.re = fmaf(a1.re, b1.re, a0.re * b0.re);
+    p.im = 0.0f;
+    return p;
+  }
+  p.re = a0.re * b0.re;
+  p.re = fmaf(-a0.im, b0.im, p.re);
+  p.re = fmaf(a1.re, b1.re, p.re);
+  p.re = fmaf(-a1.im, b1.im, p.re);
+  p.im = a0.re * b0.im;
+  p.im = fmaf(a0.im, b0.re, p.im);
+  p.im = fmaf(a1.re, b1.im, p.im);
+  p.im = fmaf(a1.im, b1.re, p.im);
+  return p;
+}
+
+__attribute__((optimize("fp-contract=off")))
+static tiny_c tiny_finish(tiny_c p, tiny_c alpha, tiny_c beta, tiny_c old, int read_c, int cplx) {
+  tiny_c t;
+  if (!cplx) {
+    t.re = read_c ? fmaf(alpha.re, p.re, beta.re * old.re) : alpha.re * p.re;
+    t.im = 0.0f;
+    return t;
+  }
+  t.re = alpha.re * p.re;
+  t.re = fmaf(-alpha.im, p.im, t.re);
+  t.im = alpha.re * p.im;
+  t.im = fmaf(alpha.im, p.re, t.im);
+  if (read_c) {
+    t.re = fmaf(beta.re, old.re, t.re);
+    t.re = fmaf(-beta.im, old.im, t.re);
+    t.im = fmaf(beta.re, old.im, t.im);
+    t.im = fmaf(beta.im, old.re, t.im);
+  }
+  return t;
+}
+
+static tiny_c tiny_load(const float *base, size_t idx, int fpe, int conj) {
+  tiny_c v;
+  v.re = base[idx * fpe];
+  v.im = fpe == 2 ? (conj ? -base[idx * fpe + 1] : base[idx * fpe + 1]) : 0.0f;
+  return v;
+}
+
+void oracle_tiny_gemm_f32(int long_is_m, int op_a, int op_b, size_t len, float alpha_r,
+                          float alpha_i, const float *a, size_t lda, size_t stride_a,
+                          const float *b, size_t ldb, size_t stride_b, float beta_r, float beta_i,
+                          float *c, size_t ldc, size_t stride_c, size_t batch, int fpe) {
+  const int cplx = fpe == 2;
+  const tiny_c alpha = {alpha_r, alpha_i}, beta = {beta_r, beta_i};
+  const int read_c = !(beta_r == 0.0f && (!cplx || beta_i == 0.0f));
+  const int ta = op_a != 0, ca = op_a == 2, tb = op_b != 0, cb = op_b == 2;
+  for (size_t bt = 0; bt < batch; bt++) {
+    const float *ab = a + bt * stride_a * fpe;
+    const float *bb = b + bt * stride_b * fpe;
+    float *cbp = c + bt * stride_c * fpe;
+    for (size_t i = 0; i < len; i++) {
+      for (size_t j = 0; j < 2; j++) {
+        /* output element (row, col) and the two (A, B) pairs along the inner dimension */
+        const size_t row = long_is_m ? i : j, col = long_is_m ? j : i;
+        tiny_c av[2], bv[2];
+        for (size_t l = 0; l < 2; l++) {
+          av[l] = tiny_load(ab, ta ? l + row * lda : row + l * lda, fpe, ca);
+          bv[l] = tiny_load(bb, tb ? col + l * ldb : l + col * ldb, fpe, cb);
+        }
+        const tiny_c p = tiny_dot2(av[0], bv[0], av[1], bv[1], cplx);
+        const size_t ci = row + col * ldc;
+        tiny_c old = {0.0f, 0.0f};
+        if (read_c) old = tiny_load(cbp, ci, fpe, 0);
+        const tiny_c t = tiny_finish(p, alpha, beta, old, read_c, cplx);
+        cbp[ci * fpe] = t.re;
+        if (cplx) cbp[ci * fpe + 1] = t.im;
+      }
+    }
+  }
+}

@@ -135,6 +135,20 @@ def gemm_f32(op_a, op_b, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc) -> None:
                            C.c_float(beta), _fp(c), C.c_size_t(ldc))
 
 
+def tiny_gemm_f32(long_is_m: bool, op_a, op_b, length, alpha, a, lda, b, ldb, beta, c, ldc,
+                  stride_a=0, stride_b=0, stride_c=0, batch=1) -> None:
+    """In-place FP32 GEMM with two-by-two inner problem on flat column-major storage, in the
+    operation order of the device kernel (bit-exact comparison)."""
+    cplx = a.dtype == np.complex64
+    al, be = complex(alpha), complex(beta)
+    lib().oracle_tiny_gemm_f32(1 if long_is_m else 0, op_a, op_b, C.c_size_t(length),
+                               C.c_float(al.real), C.c_float(al.imag), _fp(a), C.c_size_t(lda),
+                               C.c_size_t(stride_a), _fp(b), C.c_size_t(ldb),
+                               C.c_size_t(stride_b), C.c_float(be.real), C.c_float(be.imag),
+                               _fp(c), C.c_size_t(ldc), C.c_size_t(stride_c), C.c_size_t(batch),
+                               2 if cplx else 1)
+
+
 # ------------------------------------------------------------------------ TCEC model
 def split(x: np.ndarray, kind: int):
     """(hi, lo) of every float32 value; kind 0 = FP16 (lo scaled by 2^11), 1 = TF32."""

@@ -172,3 +172,36 @@ def test_generators_are_seeded(oracle):
     assert e.min() == -30 and e.max() == 10
     z = oracle.gen_unit_frobenius_complex(2, 3, 16, 16).reshape(3, -1)
     np.testing.assert_allclose((np.abs(z) ** 2).sum(axis=1), 1.0, rtol=1e-5)
+
+
+@pytest.mark.parametrize("cplx", [False, True])
+@pytest.mark.parametrize("long_is_m", [True, False])
+@pytest.mark.parametrize("op_a,op_b", [(0, 0), (1, 0), (0, 1), (2, 2)])
+def test_tiny_gemm_restatement_against_fp64(oracle, cplx, long_is_m, op_a, op_b):
+    """The FP32 restatement of the (m,2,2)/(2,n,2) route agrees with the FP64 truth to FP32
+    rounding, for every operand layout, with padded leading dimensions and a batch."""
+    length, batch, pad = 64, 3, 2
+
+    def gen(seed, count):
+        x = oracle.gen_normal(seed, count)
+        return (x + 1j * oracle.gen_normal(seed + 50, count)).astype(np.complex64) if cplx else x
+
+    a_rc = ((length, 2) if op_a == 0 else (2, length)) if long_is_m else (2, 2)
+    b_rc = (2, 2) if long_is_m else ((2, length) if op_b == 0 else (length, 2))
+    c_rc = (length, 2) if long_is_m else (2, length)
+    lda, ldb, ldc = a_rc[0] + pad, b_rc[0] + pad, c_rc[0] + pad
+    sa, sb, sc = lda * a_rc[1] + 3, ldb * b_rc[1] + 1, ldc * c_rc[1]
+    a, b, c0 = gen(1, sa * batch), gen(2, sb * batch), gen(3, sc * batch)
+    alpha, beta = ((0.5 + 0.25j), (-1.0 + 0.5j)) if cplx else (0.5, -1.0)
+    got = c0.copy()
+    oracle.tiny_gemm_f32(long_is_m, op_a, op_b, length, alpha, a, lda, b, ldb, beta, got, ldc, sa,
+                         sb, sc, batch)
+    m, n = c_rc
+    for bt in range(batch):
+        truth = oracle.gemm_f64(op_a, op_b, m, n, 2, alpha, a[bt * sa:], lda, b[bt * sb:], ldb,
+                                beta, c0[bt * sc:], ldc)
+        assert oracle.residual(truth, got[bt * sc:], ldc) < 1e-6
+    # padding rows of C are untouched
+    g2 = got.reshape(batch, c_rc[1], ldc)
+    c2 = c0.reshape(batch, c_rc[1], ldc)
+    assert np.array_equal(g2[:, :, c_rc[0]:], c2[:, :, c_rc[0]:])
