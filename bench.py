@@ -47,6 +47,12 @@ METRIC = "effective TFLOP/s of FP16TCEC SGEMM at N=16384"
 UNIT = "TFLOP/s"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM-kernel launch, from the one-pass ncu
+# capture summarised in profiles/tcec_gemm_pair_kernel_fp16tcec.md; keyed by (mode, m, n, k).
+# Algorithmic minimum for the same launch: panels 2 x 1 GiB + C read 1 GiB + C written 1 GiB.
+MEASURED_DRAM_BYTES = {("FP16TCEC", 16384, 16384, 16384): 22.97e9 + 1.16e9}
+
+
 def read_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -286,7 +292,8 @@ def run_ours(args, rank, local_rank, world):
     achieved = 2.0 * m * n_local * k / (gemm_ms_avg * 1e-3) / 1e12 if gemm_ms_avg > 0 else 0.0
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-        "frac": achieved / peak if peak else None, "traffic": None,
+        "frac": achieved / peak if peak else None,
+        "traffic": MEASURED_DRAM_BYTES.get((mode.name, m, n_local, k)),
         "kernel": "tcec_gemm_pair_kernel (tcgen05 cta_group::2, 256x256 tile per CTA pair)",
         "kernel_ms": gemm_ms_avg, "split_pass_ms": split_ms / max(groups, 1),
         "peak_source": f"{peaks['source']} dense 16-bit tensor peak "
@@ -346,7 +353,9 @@ def run_ours(args, rank, local_rank, world):
                 "parallelism": ("single GPU" if world == 1 else
                                 f"C/B column blocks over {world} GPUs, A broadcast from rank 0 "
                                 "with NCCL inside every step"),
-                "l2": "inputs (1 GiB per matrix) exceed the 126 MB L2; no explicit flush",
+                "l2": (f"A, B, C are {m * k * 4 / 2**20:.0f} + {k * n_local * 4 / 2**20:.0f} + "
+                       f"{m * n_local * 4 / 2**20:.0f} MiB per GPU against a 126 MB L2; "
+                       "no explicit flush"),
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": 2 * args.steps * (2 if mode == api.ComputeMode.AUTO else 1),

@@ -236,6 +236,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       g.dyn = dyn;
       g.tile_n = tile_n;
       g.dev_status = h->dev_status;
+      g.wave_counter = reinterpret_cast<unsigned int *>(h->dev_status + 1);
       g.debug = h->debug_buffer;
       err = use_pair ? launch_tcec_gemm_pair(g, h->cuda_stream)
                      : launch_tcec_gemm(g, h->cuda_stream);

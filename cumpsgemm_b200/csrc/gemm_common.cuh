@@ -26,6 +26,8 @@ struct GemmKernelParams {
   // and for the accumulator drain [1], the producer for a free stage [2], drain warp 4 for
   // a finished chunk [3]; MMA loop cycles [4]; contributing CTAs [5].
   unsigned long long *debug;
+  // Pair kernel, nullable: arrivals of clusters at tile starts (see the kernel's producer).
+  unsigned int *wave_counter;
   // Stages whose hi*hi products accumulate in TMEM before one drain (pair kernel; 1 or 2).
   uint32_t drain_chunk;
   // Pair tiles in the whole launch (tiles_m * tiles_n * batch); the persistent pair kernel
@@ -33,8 +35,9 @@ struct GemmKernelParams {
   uint32_t total_tiles;
 };
 
-// Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {128 bytes of K, box_rows, 1},
-// 128-byte swizzle.  Returns false if the driver entry point is unavailable or rejects it.
+// Tensor map over a K-blocked panel: dims {elements per 128 bytes, rows_pad, planes * k_blocks},
+// box {128 bytes of K, box_rows, 1}, 128-byte swizzle; a load's coordinates are
+// (0, first row, plane * k_blocks + K block).  Returns false if the driver entry point is unavailable or rejects it.
 bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_t k_pad,
                     uint32_t rows_pad, uint32_t planes, uint32_t box_rows);
 

@@ -69,7 +69,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
   ok &= cudaMalloc(&h->dyn_launch.flag_buffer, sizeof(int) * h->dyn_launch.flag_buffer_length) ==
         cudaSuccess;
   ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
-  ok &= cudaMalloc(&h->dev_status, sizeof(int)) == cudaSuccess;
+  ok &= cudaMalloc(&h->dev_status, 2 * sizeof(int)) == cudaSuccess; // status, wave counter
   if (!ok) {
     cuMpSGEMM_destroy(h);
     return CUBLAS_STATUS_ALLOC_FAILED;
@@ -81,7 +81,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
   cudaMemsetAsync(es.dev_mode, 0, sizeof(int) * es.buffer_length, h->cuda_stream);
   cudaMemsetAsync(h->dyn_launch.flag_buffer, 0, sizeof(int) * h->dyn_launch.flag_buffer_length,
                   h->cuda_stream);
-  cudaMemsetAsync(h->dev_status, 0, sizeof(int), h->cuda_stream);
+  cudaMemsetAsync(h->dev_status, 0, 2 * sizeof(int), h->cuda_stream);
   configure_mode_buffer(h);
   init_flag_buffer(h);
   if (cudaStreamSynchronize(h->cuda_stream) != cudaSuccess) {

@@ -110,7 +110,7 @@ struct cuMpSGEMM_handle {
   std::size_t workspace_limit_bytes = 0; // 0 = derive from free memory
 
   // Device status word the GEMM kernel writes when a bounded wait gives up.
-  int *dev_status = nullptr;
+  int *dev_status = nullptr; // [0] kernel status word, [1] wave counter of the pair kernel
 
   // Optional per-launch timing: events recorded on the launching stream before the split
   // pass, between split pass and GEMM kernel, and after the GEMM kernel.
@@ -186,6 +186,9 @@ struct TcecGemmArgs {
   int tile_n;           // 256, 128 or 64
   int *dev_status;
   unsigned long long *debug = nullptr; // optional stall breakdown buffer (8 x u64)
+  // Optional device word the persistent pair kernel uses to keep its clusters in step
+  // (zeroed by the launcher before every launch); null switches the pacing off.
+  unsigned int *wave_counter = nullptr;
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
 // Self-test of the bounded mbarrier wait (see cuMpSGEMM_selftest_bounded_wait).

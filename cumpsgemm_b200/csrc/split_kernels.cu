@@ -11,10 +11,13 @@
 //   TF32:  hi = RNA_tf32(v), lo = RNA_tf32(v - hi)
 // where v = x * scale (scale is an exact power of two, 1 when no scaling).
 //
-// Panel layout (element type half or float):
-//   panel[((b * planes + z) * rows_pad + r) * k_pad + kk],  z = 0 (hi), 1 (lo)
-// rows_pad / k_pad are multiples of 64 and every padding element is written
-// as zero on every call, so the GEMM kernel needs no edge handling.
+// Panel layout (element type half or float), blocked along K in units of 128 bytes
+// (KBE = 64 half or 32 float elements), z = 0 (hi), 1 (lo):
+//   panel[(((b * planes + z) * (k_pad / KBE) + kk / KBE) * rows_pad + r) * KBE + kk % KBE]
+// so the 128-byte K slices of consecutive rows are contiguous: the box one TMA load of the
+// GEMM kernel fetches (128 rows x 128 bytes) is one 16 KiB run of memory instead of 128 lines
+// a whole panel row apart.  rows_pad / k_pad are multiples of 64 and every padding element is
+// written as zero on every call, so the GEMM kernel needs no edge handling.
 //
 // Complex operands are expanded to real ones so that the GEMM kernel is a real
 // GEMM producing interleaved (re, im) rows of C:
@@ -35,6 +38,13 @@ __device__ __forceinline__ float to_tf32(float v) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
   return __uint_as_float(r);
+}
+
+// Offset of element (r, kk) inside one plane of a panel (see the layout above).
+template <int KIND>
+__device__ __forceinline__ uint64_t panel_offset(uint64_t r, uint64_t kk, uint32_t rows_pad) {
+  constexpr uint64_t KBE = (KIND == 0) ? 64 : 32;
+  return ((kk / KBE) * rows_pad + r) * KBE + (kk % KBE);
 }
 
 struct SplitParams {
@@ -128,7 +138,7 @@ __device__ __forceinline__ void split_generic_body(const SplitParams &p, const u
         v[j] = (!im_row && odd) ? -x : x;
       }
     }
-    const uint64_t out_off = (er0 + er) * p.k_pad + ek0 + ek;
+    const uint64_t out_off = panel_offset<KIND>(er0 + er, ek0 + ek, p.rows_pad);
     if constexpr (KIND == 0) {
       __align__(16) __half hi[8];
       __align__(16) __half lo[8];
@@ -242,7 +252,8 @@ __device__ __forceinline__ void split_kcontig_body(const SplitParams &p, const u
     const float v[8] = {x[i][0].x * scale, x[i][0].y * scale, x[i][0].z * scale, x[i][0].w * scale,
                         x[i][1].x * scale, x[i][1].y * scale, x[i][1].z * scale, x[i][1].w * scale};
     convert_store8<KIND>(v, p.panel,
-                         static_cast<uint64_t>(b) * p.planes * plane_elems + r * p.k_pad + k0,
+                         static_cast<uint64_t>(b) * p.planes * plane_elems +
+                             panel_offset<KIND>(r, k0, p.rows_pad),
                          plane_elems, p.planes);
   }
 }
@@ -288,8 +299,8 @@ __device__ __forceinline__ void split_rcontig_body(const SplitParams &p, const u
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = tile[er][ek + j];
     convert_store8<KIND>(v, p.panel,
-                         static_cast<uint64_t>(b) * p.planes * plane_elems + (r0 + er) * p.k_pad +
-                             k0 + ek,
+                         static_cast<uint64_t>(b) * p.planes * plane_elems +
+                             panel_offset<KIND>(r0 + er, k0 + ek, p.rows_pad),
                          plane_elems, p.planes);
   }
 }

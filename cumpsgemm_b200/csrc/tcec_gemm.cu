@@ -63,7 +63,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   using Cfg = TileCfg<BN, EC>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
-  constexpr int BK = ROW_BYTES / ELEM_BYTES; // elements of K per stage
   constexpr int K_STEPS = ROW_BYTES / 32;    // tcgen05.mma consumes 32 bytes of K per instruction
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, BM, BN);
@@ -141,15 +140,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t fb = ptx::smem_u32(&full_bar[s]);
         ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
         uint8_t *st = smem + s * Cfg::STAGE_BYTES;
-        const int kc = static_cast<int>(kb * BK);
-        ptx::tma_load_3d(ptx::smem_u32(st), &map_a, fb, kc, m0, za);
+        // coordinates: (element in the K block, row, plane * k_blocks + K block)
+        const int zh = static_cast<int>(static_cast<uint32_t>(za) * k_blocks + kb);
+        ptx::tma_load_3d(ptx::smem_u32(st), &map_a, fb, 0, m0, zh);
         if constexpr (EC) {
-          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_a, fb, kc, m0, za + 1);
-          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE), &map_b, fb, kc, n0, za);
-          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE + Cfg::B_TILE), &map_b, fb, kc, n0,
-                           za + 1);
+          const int zl = zh + static_cast<int>(k_blocks);
+          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_a, fb, 0, m0, zl);
+          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE), &map_b, fb, 0, n0, zh);
+          ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE + Cfg::B_TILE), &map_b, fb, 0, n0,
+                           zl);
         } else {
-          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_b, fb, kc, n0, za);
+          ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_b, fb, 0, n0, zh);
         }
       }
       if (dbg) atomicAdd(p.debug + 2, dbg_wait);
@@ -328,16 +329,18 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// Tensor map over a panel: dims {k_pad, rows_pad, planes}, box {BK, box_rows, 1}, 128-byte swizzle.
+// Tensor map over a K-blocked panel (layout: split_kernels.cu); see gemm_common.cuh.
 bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_t k_pad,
                     uint32_t rows_pad, uint32_t planes, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   const uint32_t es = (kind == SplitKind::fp16) ? 2u : 4u;
-  const cuuint64_t dims[3] = {k_pad, rows_pad, planes};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k_pad) * es,
-                                 static_cast<cuuint64_t>(k_pad) * es * rows_pad};
-  const cuuint32_t box[3] = {ROW_BYTES / es, box_rows, 1};
+  // K-blocked panel: 128-byte K slices of all rows of one K block are contiguous.
+  const uint32_t kbe = ROW_BYTES / es;
+  const uint32_t k_blocks = k_pad / kbe;
+  const cuuint64_t dims[3] = {kbe, rows_pad, static_cast<cuuint64_t>(planes) * k_blocks};
+  const cuuint64_t strides[2] = {ROW_BYTES, static_cast<cuuint64_t>(ROW_BYTES) * rows_pad};
+  const cuuint32_t box[3] = {kbe, box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt =
       (kind == SplitKind::fp16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -389,6 +392,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   p.dyn = a.dyn;
   p.status = a.dev_status;
   p.debug = a.debug;
+  p.wave_counter = nullptr;
   p.drain_chunk = 1;
   p.total_tiles = 0;
   const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;

@@ -82,7 +82,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
   constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
-  constexpr int BK = ROW_BYTES / ELEM_BYTES;
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, 2 * BM_CTA, BN_PAIR);
@@ -145,10 +144,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     if (lane == 0) {
       uint32_t it = 0; // stage uses since kernel start, across tiles
       bool ok = true;
-      for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters) {
+      bool pace = leader && p.wave_counter != nullptr && total_tiles > num_clusters;
+      uint32_t wave = 0;
+      for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++wave) {
         const TileCoord tc = tile_coord(tile, p, rank);
         const int za = static_cast<int>(tc.batch * 2u);
         const int nb0 = tc.n0 + static_cast<int>(rank) * 128; // this CTA's rows of the B tile
+        if (pace) {
+          // Keep the clusters in step.  Clusters that run at the same time share panel rows
+          // through L2 only while they are at about the same k; left alone they drift apart
+          // by about 2 % per tile and, once the drift exceeds what L2 retains, most loads go
+          // to DRAM (measured at m=n=k=16384: 88 GB read per launch against 4 GB of panels
+          // and C).  So every cluster announces each tile start and waits until all clusters
+          // of the wave have.  The wait is only a pacing aid: it gives up after 100 us, and
+          // then this cluster stops pacing for the rest of the launch, so clusters that are
+          // not resident at the same time cost one time-out and never a wrong result.
+          atomicAdd(p.wave_counter, 1u);
+          const uint32_t target = min(total_tiles, (wave + 1) * num_clusters);
+          const uint64_t t0 = ptx::globaltimer_ns();
+          while (*reinterpret_cast<volatile unsigned int *>(p.wave_counter) < target) {
+            if (ptx::globaltimer_ns() - t0 > 100000ull) {
+              pace = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
         for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -159,11 +180,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
           if (leader) ptx::mbar_arrive_expect_tx(fb_local, 2 * STAGE_BYTES);
           const uint32_t fb = ptx::map_to_cta(fb_local, 0); // the leader's barrier
           const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
-          const int kc = static_cast<int>(kb * BK);
-          ptx::tma_load_3d_pair(st, &map_a, fb, kc, tc.m0, za);
-          ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, kc, tc.m0, za + 1);
-          ptx::tma_load_3d_pair(st + 2 * TILE_BYTES, &map_b, fb, kc, nb0, za);
-          ptx::tma_load_3d_pair(st + 3 * TILE_BYTES, &map_b, fb, kc, nb0, za + 1);
+          // coordinates: (element in the K block, row, plane * k_blocks + K block); each box
+          // is one contiguous 16 KiB run of the K-blocked panel
+          const int zh = static_cast<int>(static_cast<uint32_t>(za) * k_blocks + kb);
+          const int zl = zh + static_cast<int>(k_blocks);
+          ptx::tma_load_3d_pair(st, &map_a, fb, 0, tc.m0, zh);
+          ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, 0, tc.m0, zl);
+          ptx::tma_load_3d_pair(st + 2 * TILE_BYTES, &map_b, fb, 0, nb0, zh);
+          ptx::tma_load_3d_pair(st + 3 * TILE_BYTES, &map_b, fb, 0, nb0, zl);
         }
       }
       if (dbg) atomicAdd(p.debug + 2, dbg_wait);
@@ -416,6 +440,15 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   p.total_tiles = static_cast<uint32_t>(total);
   const uint32_t clusters = static_cast<uint32_t>(
       total < static_cast<uint64_t>(max_clusters[dev]) ? total : max_clusters[dev]);
+  p.wave_counter = nullptr;
+  if (a.wave_counter != nullptr && total > clusters) {
+    const char *e = std::getenv("CUMPSGEMM_PACE");
+    if (e == nullptr || std::atoi(e) != 0) {
+      const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
+      if (me != cudaSuccess) return me;
+      p.wave_counter = a.wave_counter;
+    }
+  }
   kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
