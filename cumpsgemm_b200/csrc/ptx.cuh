@@ -109,6 +109,11 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity,
   return ok;
 }
 
+// Hint: bring the cache line at p into L2.
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -267,24 +267,37 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                               : p.c + static_cast<uint64_t>(batch_id) * p.stride_c) +
                      row;
       const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
+      // Columns go in groups: all loads of a group are issued before its first store (the
+      // compiler must assume a store may alias the next load, which would put one memory
+      // latency per column on the tile's critical path when beta != 0).
+      constexpr int EPI_BATCH = (CPT >= 8) ? 8 : CPT;
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) {
-        const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i);
-        if (col < p.n) { // uniform over the warp
-          float *cp = cbase + static_cast<uint64_t>(col) * p.ldc;
-          float old = 0.f;
-          if (read_c && row_ok) old = *cp;
-          float out;
-          if (p.is_complex) {
-            const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
-            const float old_o = __shfl_xor_sync(0xffffffffu, old, 1);
-            out = ar * acc[i] + sgn * ai * acc_o;
-            if (read_c) out += br * old + sgn * bi * old_o;
-          } else {
-            out = ar * acc[i];
-            if (read_c) out = fmaf(br, old, out);
+      for (int i0 = 0; i0 < CPT; i0 += EPI_BATCH) {
+        float old[EPI_BATCH];
+#pragma unroll
+        for (int j = 0; j < EPI_BATCH; ++j) {
+          const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i0 + j);
+          old[j] = (read_c && row_ok && col < p.n)
+                       ? __ldcs(cbase + static_cast<uint64_t>(col) * p.ldc)
+                       : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < EPI_BATCH; ++j) {
+          const int i = i0 + j;
+          const uint32_t col = static_cast<uint32_t>(n0) + col_base + static_cast<uint32_t>(i);
+          if (col < p.n) { // uniform over the warp
+            float out;
+            if (p.is_complex) {
+              const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
+              const float old_o = __shfl_xor_sync(0xffffffffu, old[j], 1);
+              out = ar * acc[i] + sgn * ai * acc_o;
+              if (read_c) out += br * old[j] + sgn * bi * old_o;
+            } else {
+              out = ar * acc[i];
+              if (read_c) out = fmaf(br, old[j], out);
+            }
+            if (row_ok) cbase[static_cast<uint64_t>(col) * p.ldc] = out;
           }
-          if (row_ok) *cp = out;
         }
       }
     }

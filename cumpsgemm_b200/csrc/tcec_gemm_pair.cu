@@ -39,6 +39,7 @@ constexpr uint32_t D1_COL = 256;
 constexpr int TILE_BYTES = 128 * ROW_BYTES; // every sub-tile is 128 rows
 constexpr int STAGE_BYTES = 4 * TILE_BYTES; // A_hi, A_lo, B_hi, B_lo
 constexpr int STAGES = 3;
+constexpr uint32_t C_PREFETCH_LEAD = 8; // drain chunks between the L2 prefetch of C and its use
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 template <int KIND>
@@ -81,7 +82,6 @@ template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
-  constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, 2 * BM_CTA, BN_PAIR);
@@ -283,7 +283,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
       for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
 
+      // C(row, col): lanes hold consecutive rows of the column-major C, so each warp access
+      // covers 128 contiguous bytes of one column.
+      const uint32_t row =
+          static_cast<uint32_t>(tc.m0) + quarter * 32u + static_cast<uint32_t>(lane);
+      const bool row_ok = row < p.m;
+      float *cbase = ((p.c_array != nullptr) ? p.c_array[tc.batch]
+                                              : p.c + static_cast<uint64_t>(tc.batch) * p.stride_c) +
+                     row;
+      const uint32_t prefetch_at = (n_chunks > C_PREFETCH_LEAD) ? n_chunks - C_PREFETCH_LEAD : 0u;
+
       for (uint32_t c = 0; c < n_chunks; ++c, ++chunk_idx) {
+        if (read_c && c == prefetch_at) {
+          // beta != 0: pull this warp's part of the C tile into L2 a few chunks before the
+          // epilogue reads it (lane l fetches the line of columns l, l+32, ...)
+#pragma unroll
+          for (int q = 0; q < CPT / 32; ++q) {
+            const uint32_t col = static_cast<uint32_t>(tc.n0) + col_base +
+                                 static_cast<uint32_t>(q * 32 + lane);
+            if (col < p.n && row - lane < p.m)
+              ptx::prefetch_l2(cbase - lane + static_cast<uint64_t>(col) * p.ldc);
+          }
+        }
         ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_full), chunk_idx & 1u, abort_flag, p.status,
                                   ptx::kErrWaitD0Full, dbg, &dbg_wait);
         if (!ok) break;
@@ -320,32 +341,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(d1_empty_leader);
 
-      // C(row, col) = alpha * acc + beta * C(row, col); lanes hold consecutive rows of the
-      // column-major C, so each warp store covers 128 contiguous bytes.
-      const uint32_t row =
-          static_cast<uint32_t>(tc.m0) + quarter * 32u + static_cast<uint32_t>(lane);
-      const bool row_ok = row < p.m;
-      float *cbase = ((p.c_array != nullptr) ? p.c_array[tc.batch]
-                                              : p.c + static_cast<uint64_t>(tc.batch) * p.stride_c) +
-                     row;
+      // C(row, col) = alpha * acc + beta * C(row, col)
+      // Columns go in groups of EPI_BATCH: all loads of a group are issued before its first
+      // store, otherwise every load would wait for the store before it (the compiler must
+      // assume they alias) and a tile would spend 128 memory latencies here.
+      constexpr int EPI_BATCH = 8;
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) {
-        const uint32_t col = static_cast<uint32_t>(tc.n0) + col_base + static_cast<uint32_t>(i);
-        if (col < p.n) { // uniform over the warp
-          float *cp = cbase + static_cast<uint64_t>(col) * p.ldc;
-          float old = 0.f;
-          if (read_c && row_ok) old = *cp;
-          float out;
-          if (p.is_complex) {
-            const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
-            const float old_o = __shfl_xor_sync(0xffffffffu, old, 1);
-            out = ar * acc[i] + sgn * ai * acc_o;
-            if (read_c) out += br * old + sgn * bi * old_o;
-          } else {
-            out = ar * acc[i];
-            if (read_c) out = fmaf(br, old, out);
+      for (int i0 = 0; i0 < CPT; i0 += EPI_BATCH) {
+        float old[EPI_BATCH];
+#pragma unroll
+        for (int j = 0; j < EPI_BATCH; ++j) {
+          const uint32_t col =
+              static_cast<uint32_t>(tc.n0) + col_base + static_cast<uint32_t>(i0 + j);
+          old[j] = (read_c && row_ok && col < p.n)
+                       ? __ldcs(cbase + static_cast<uint64_t>(col) * p.ldc)
+                       : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < EPI_BATCH; ++j) {
+          const int i = i0 + j;
+          const uint32_t col = static_cast<uint32_t>(tc.n0) + col_base + static_cast<uint32_t>(i);
+          if (col < p.n) { // uniform over the warp
+            float out;
+            if (p.is_complex) {
+              const float acc_o = __shfl_xor_sync(0xffffffffu, acc[i], 1);
+              const float old_o = __shfl_xor_sync(0xffffffffu, old[j], 1);
+              out = ar * acc[i] + sgn * ai * acc_o;
+              if (read_c) out += br * old[j] + sgn * bi * old_o;
+            } else {
+              out = ar * acc[i];
+              if (read_c) out = fmaf(br, old[j], out);
+            }
+            if (row_ok) cbase[static_cast<uint64_t>(col) * p.ldc] = out;
           }
-          if (row_ok) *cp = out;
         }
       }
     }
