@@ -30,6 +30,8 @@ struct GemmKernelParams {
   unsigned int *wave_counter;
   // Stages whose hi*hi products accumulate in TMEM before one drain (pair kernel; 1 or 2).
   uint32_t drain_chunk;
+  // Stages in the first chunk of every tile (pair kernel; >= drain_chunk).
+  uint32_t first_chunk;
   // Pair tiles in the whole launch (tiles_m * tiles_n * batch); the persistent pair kernel
   // walks them with a stride of the number of clusters in the grid.
   uint32_t total_tiles;

@@ -407,6 +407,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   p.debug = a.debug;
   p.wave_counter = nullptr;
   p.drain_chunk = 1;
+  p.first_chunk = 1;
   p.total_tiles = 0;
   const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
   if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;

@@ -39,6 +39,7 @@ constexpr uint32_t D1_COL = 256;
 constexpr int TILE_BYTES = 128 * ROW_BYTES; // every sub-tile is 128 rows
 constexpr int STAGE_BYTES = 4 * TILE_BYTES; // A_hi, A_lo, B_hi, B_lo
 constexpr int STAGES = 3;
+constexpr uint32_t kPaceMinStages = 32; // shortest K loop (in stages) that is paced
 constexpr uint32_t C_PREFETCH_LEAD = 8; // drain chunks between the L2 prefetch of C and its use
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
@@ -201,17 +202,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       const long long dbg_t0 = clock64();
       const uint32_t chunk = p.drain_chunk;
+      const uint32_t first = p.first_chunk; // stages in the first chunk of every tile
+      // Chunks of a tile: [0, first), then pieces of `chunk` stages.
+      auto chunk_start = [&](uint32_t kb) {
+        return kb == 0 || (kb >= first && (kb - first) % chunk == 0);
+      };
       uint32_t it = 0, chunk_idx = 0, tile_iter = 0;
       for (uint32_t tile = cluster_id; tile < total_tiles && ok;
            tile += num_clusters, ++tile_iter) {
-        uint32_t in_chunk = 0;
         for (uint32_t kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+          const bool first_in_chunk = chunk_start(kb);
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = ptx::mbar_wait_timed(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
                                     ptx::kErrWaitFull, dbg, &dbg_wait);
           if (!ok) break;
-          if (in_chunk == 0) {
+          if (first_in_chunk) {
             // D0 of the previous chunk must have been drained before it is overwritten.
             ok = ptx::mbar_wait_timed(ptx::smem_u32(d0_empty), (chunk_idx & 1u) ^ 1u, abort_flag,
                                       p.status, ptx::kErrWaitD0Empty, dbg, &dbg_wait2);
@@ -226,8 +232,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
           for (int ks = 0; ks < K_STEPS; ++ks)
             mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
-                           (in_chunk > 0 || ks > 0) ? 1u : 0u);
-          const bool last_in_chunk = (in_chunk + 1 == chunk) || (kb + 1 == k_blocks);
+                           (!first_in_chunk || ks > 0) ? 1u : 0u);
+          const bool last_in_chunk = (kb + 1 == k_blocks) || chunk_start(kb + 1);
           if (last_in_chunk) ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
           if (kb == 0) {
             // D1 still holds the previous tile's corrections until its epilogue has read them.
@@ -243,12 +249,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
           for (int ks = 0; ks < K_STEPS; ++ks)
             mma_pair<KIND>(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
           ptx::tc_commit_pair(ptx::smem_u32(&empty_bar[s]), BOTH);
-          if (last_in_chunk) {
-            in_chunk = 0;
-            ++chunk_idx;
-          } else {
-            ++in_chunk;
-          }
+          if (last_in_chunk) ++chunk_idx;
         }
         if (ok) ptx::tc_commit_pair(ptx::smem_u32(d1_full), BOTH);
       }
@@ -267,7 +268,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     const uint32_t col_base = half * CPT;
     const uint32_t d0_empty_leader = ptx::map_to_cta(ptx::smem_u32(d0_empty), 0);
     const uint32_t d1_empty_leader = ptx::map_to_cta(ptx::smem_u32(d1_empty), 0);
-    const uint32_t n_chunks = (k_blocks + p.drain_chunk - 1) / p.drain_chunk;
+    const uint32_t n_chunks =
+        1u + ((k_blocks > p.first_chunk)
+                  ? (k_blocks - p.first_chunk + p.drain_chunk - 1) / p.drain_chunk
+                  : 0u);
     const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
     const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
     const float br = p.beta_r, bi = p.beta_i;
@@ -460,6 +464,25 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     // uniform(-1,1): residual 3.1e-7 / 2.8e-7 / 3.7e-7 / 6.5e-7 / 2.5e-6 / 1.9e-5 for 1 / 2 / 4 /
     // 8 / 32 / 256 stages per drain (FP32 cuBLAS SGEMM on the same inputs: 2.3e-6).
     p.drain_chunk = (v >= 1) ? static_cast<uint32_t>(v) : 2u;
+    // The first chunk of every tile is longer: while it accumulates, the epilogue warps are
+    // still storing the previous tile, and the issuer would otherwise wait about 17,000 cycles
+    // per tile for them to drain a short first chunk (measured: 5 % of a tile at k=16384, 18 %
+    // at k=4096).  Its length is bounded by accuracy: the tensor core's own accumulation loses
+    // about 1.2e-9 relative accuracy per accumulated k value, and the first chunk's share of
+    // the result is sqrt(first / k), so the result stays as close to the FP64 product as with
+    // short chunks only if first^1.5 <= ~80 sqrt(k).  Measured residuals (FP16TCEC, m=n=4096,
+    // FP32 cuBLAS in brackets): k=512 with 128 / 256 / 512 values in the first chunk 2.0e-7 /
+    // 2.8e-7 / 6.5e-7 (4.1e-7); k=4096 with 256 / 512: 2.3e-7 / 3.1e-7 (1.2e-6); k=16384 with
+    // 128 / 512 / 1024: 2.8e-7 / 3.0e-7 / 4.2e-7 (2.3e-6).  TF32 products carry more bits into
+    // the accumulator and lose twice as much, so that kind gets half the length.
+    const uint32_t k_per_stage = ROW_BYTES / es;
+    const uint32_t k_total = p.k_blocks * k_per_stage;
+    uint32_t first_k = (k_total >= 8192u) ? 512u : (k_total >= 2048u ? 256u : 128u);
+    if (a.kind != SplitKind::fp16) first_k /= 2u;
+    const char *f = std::getenv("CUMPSGEMM_FIRST_CHUNK");
+    const int fv = (f != nullptr) ? std::atoi(f) : 0;
+    p.first_chunk = (fv >= 1) ? static_cast<uint32_t>(fv) : first_k / k_per_stage;
+    if (p.first_chunk < p.drain_chunk) p.first_chunk = p.drain_chunk;
   }
   const uint64_t total = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
   if (total == 0 || total > 0x7fffffffull) return cudaErrorInvalidValue;
@@ -469,7 +492,9 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   const uint32_t clusters = static_cast<uint32_t>(
       total < static_cast<uint64_t>(max_clusters[dev]) ? total : max_clusters[dev]);
   p.wave_counter = nullptr;
-  if (a.wave_counter != nullptr && total > clusters) {
+  // Pacing pays when tiles are long (the drift it removes is 2 % of a tile) and clusters share
+  // panel rows; for short tiles a barrier per tile costs more than it saves.
+  if (a.wave_counter != nullptr && total > clusters && p.k_blocks >= kPaceMinStages) {
     const char *e = std::getenv("CUMPSGEMM_PACE");
     if (e == nullptr || std::atoi(e) != 0) {
       const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
