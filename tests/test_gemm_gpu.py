@@ -283,6 +283,39 @@ def test_large_size_against_sampled_fp64(handle, oracle, n):
     assert diff.item() < oracle.error_threshold(True, n)
 
 
+def test_scheduling_aids_do_not_change_results(handle, oracle):
+    """Wave pacing only delays tile starts and repeated calls take the same path: a GEMM with
+    several waves of tiles per cluster and a long K loop gives the same bits with pacing on,
+    with pacing off, and on a second call; the kernel's status word stays clear."""
+    torch = _torch()
+    m, n, k = 4096, 8192, 2560            # 512 pair tiles (about 7 waves), 40 K stages
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+    a = torch.rand(m * k, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(k * n, device="cuda", generator=g) * 2 - 1
+    c0 = torch.rand(m * n, device="cuda", generator=g) * 2 - 1
+    outs = []
+    old = os.environ.get("CUMPSGEMM_PACE")
+    try:
+        for pace in ("1", "0", "1"):
+            os.environ["CUMPSGEMM_PACE"] = pace
+            c = c0.clone()
+            handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c, m, FP16TCEC)
+            outs.append(c)
+    finally:
+        if old is None:
+            os.environ.pop("CUMPSGEMM_PACE", None)
+        else:
+            os.environ["CUMPSGEMM_PACE"] = old
+    assert handle.kernel_status() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    # and the result is right: sampled columns against the FP64 oracle
+    ah, bh, c0h, ch = (x.cpu().numpy() for x in (a, b, c0, outs[0]))
+    for j in (0, 300, n - 1):
+        truth = oracle.gemm_f64(N, N, m, 1, k, 1.0, ah, m, bh[j * k:], k, 0.5, c0h[j * m:], m)
+        assert oracle.residual(truth, ch[j * m:(j + 1) * m], m) < oracle.error_threshold(True, k)
+
+
 def test_host_buffer_gemm_pipelined_matches_resident(handle, oracle):
     """api.HostGemm (pinned host operands, column-block pipeline) against the resident call."""
     from cumpsgemm_b200 import api
