@@ -53,26 +53,43 @@ template <> struct Scalar<cuComplex> {
   static float im(const cuComplex *p) { return p->y; }
 };
 
-// Tile width for a problem (CUMPSGEMM_TILE_N overrides).  256 means the CTA-pair kernel's
-// 256 x 256 tile when the mode is error-corrected.  Measured on B200 (GEMM kernel only, us):
-//   m=n=k   BN=64   BN=128   pairs
-//   1024     22.1    24.8     34.0      (16 pair tiles)
-//   2048    116      71.0     59.4      (64 pair tiles on 74 pair slots)
-//   4096    805     407      335
-// so the wide tile wins from about two thirds of a wave upwards; narrower tiles move the same
-// operand bytes for fewer MMAs and only pay off when they are needed to occupy the GPU.
-int pick_tile_n(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
-                std::uint64_t batch) {
+// Tile for a problem: width 256 / 128 / 64 of the single-CTA kernel (128 rows), or the CTA-pair
+// kernel's 256 x 256 tile (error-corrected modes only).  CUMPSGEMM_TILE_N forces the width,
+// CUMPSGEMM_PAIR=0/1 the kernel.  Measured on B200 (GEMM kernel only, us, FP16TCEC, beta=0.5,
+// 30 calls back to back):
+//   m=n=k   128x64   128x128   128x256   pairs 256x256
+//   1024     22.0     24.4      32.4       37.0      (16 pair tiles)
+//   1536     50.4     31.3      40.8       46.7      (36)
+//   2048    121       76.3      56.7       65.9      (64 pair tiles on 74 pair slots)
+//   3072      -      198       155        154        (144)
+//   4096      -      449       384        362        (256)
+// The pair kernel wins once there is more than one wave of pair tiles; below that the widest
+// single-CTA tile that still gives about two thirds of the SMs a tile is fastest: narrower
+// tiles move the same operand bytes for fewer MMAs.
+struct TileChoice {
+  int tile_n;
+  bool pair;
+};
+
+TileChoice pick_tile(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
+                     std::uint64_t batch, bool ec) {
+  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
+  const bool pair_off = pair_env != nullptr && pair_env[0] == '0';
+  const bool pair_on = pair_env != nullptr && pair_env[0] == '1';
   const char *force = std::getenv("CUMPSGEMM_TILE_N");
   if (force != nullptr) {
     const int v = std::atoi(force);
-    if (v == 256 || v == 128 || v == 64) return v;
+    if (v == 256) return {256, ec && !pair_off};
+    if (v == 128 || v == 64) return {v, false};
   }
+  const std::uint64_t sms = static_cast<std::uint64_t>(h->num_sms);
   const std::uint64_t pair_tiles = ((m_exp + 255) / 256) * ((n + 255) / 256) * batch;
-  if (3 * pair_tiles >= h->num_sms) return 256; // >= 2/3 of the num_sms/2 pair slots
+  const std::uint64_t tiles_256 = ((m_exp + 127) / 128) * ((n + 255) / 256) * batch;
   const std::uint64_t tiles_128 = ((m_exp + 127) / 128) * ((n + 127) / 128) * batch;
-  if (tiles_128 >= h->num_sms) return 128;
-  return 64;
+  if (ec && !pair_off && (pair_on || pair_tiles > sms / 2)) return {256, true};
+  if (3 * tiles_256 >= 2 * sms) return {256, false};
+  if (3 * tiles_128 >= 2 * sms) return {128, false};
+  return {64, false};
 }
 
 } // namespace
@@ -138,14 +155,12 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   const std::uint64_t fpe = is_complex ? 2 : 1;
   const std::uint64_t m_exp = m * fpe; // rows of the expanded real problem
   const std::uint64_t k_exp = k * fpe;
-  const int tile_n = pick_tile_n(h, m_exp, n, batch);
+  const TileChoice choice = pick_tile(h, m_exp, n, batch, ec);
+  const int tile_n = choice.tile_n;
+  const bool use_pair = choice.pair;
   if (used_kernel_module_id != nullptr)
     *used_kernel_module_id = (tile_n == 256) ? 0u : (tile_n == 128 ? 1u : 2u);
 
-  // 256 x 256 tiles on CTA pairs whenever the wide tile is chosen for an error-corrected
-  // mode (CUMPSGEMM_PAIR=0 forces the single-CTA kernel).
-  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
-  const bool use_pair = ec && tile_n == 256 && !(pair_env != nullptr && pair_env[0] == '0');
   const std::uint32_t rows_pad_a =
       static_cast<std::uint32_t>(round_up(m_exp, use_pair ? 256 : 128));
   const std::uint32_t rows_pad_b = static_cast<std::uint32_t>(round_up(n, tile_n));
