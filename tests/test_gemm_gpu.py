@@ -316,6 +316,47 @@ def test_scheduling_aids_do_not_change_results(handle, oracle):
         assert oracle.residual(truth, ch[j * m:(j + 1) * m], m) < oracle.error_threshold(True, k)
 
 
+def test_calls_replay_from_a_cuda_graph(oracle):
+    """After one warm-up call of the same shape (workspace, kernel attributes and occupancy
+    queries are set up then) a GEMM call is launches and one 4-byte memset only, so it can be
+    captured into a CUDA graph; replays give the bits of the direct call, also after the
+    inputs changed in place."""
+    torch = _torch()
+    from cumpsgemm_b200 import api
+
+    h = api.Handle()
+    m, n, k = 2304, 2048, 2560      # more than one wave of pair tiles: paced pair kernel
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    a = torch.rand(m * k, device="cuda", generator=g) * 2 - 1
+    b = torch.rand(k * n, device="cuda", generator=g) * 2 - 1
+    c = torch.zeros(m * n, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        h.use_current_torch_stream()
+        for mode in (FP16TCEC, TF32TCEC):
+            h.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, mode)       # warm-up
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    for mode in (FP16TCEC, TF32TCEC):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            h.use_current_torch_stream()
+            h.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, mode)
+        for scale in (1.0, 0.5):
+            a.mul_(scale)
+            graph.replay()
+            torch.cuda.synchronize()
+            replayed = c.clone()
+            h.use_current_torch_stream()
+            h.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, mode)
+            torch.cuda.synchronize()
+            assert torch.equal(replayed, c)
+    assert h.kernel_status() == 0
+    h.destroy()
+
+
 def test_host_buffer_gemm_pipelined_matches_resident(handle, oracle):
     """api.HostGemm (pinned host operands, column-block pipeline) against the resident call."""
     from cumpsgemm_b200 import api
