@@ -93,7 +93,8 @@ struct TinyArgs {
   const void *a, *b;
   void *c;
   uint64_t lda, ldb, ldc, stride_a, stride_b, stride_c;
-  uint64_t len;     // the long dimension (m or n)
+  uint64_t len;     // the long dimension (m or n), a power of two
+  uint32_t log2_len;
   uint64_t batch;
   bool trans_a, conj_a, trans_b, conj_b, read_c;
 };
@@ -112,57 +113,63 @@ tiny_gemm_kernel(TinyArgs g, typename scalar_of<T>::type alpha, typename scalar_
   const uint64_t step = static_cast<uint64_t>(gridDim.x) * blockDim.x;
   for (uint64_t t0 = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; t0 < total;
        t0 += step * kUnroll) {
-    S x0[kUnroll], x1[kUnroll];   // the two values along the inner dimension of the long operand
-    S q[kUnroll][4];              // the 2 x 2 operand: q[.][2*j + l] = value (l, j) resp. (r, l)
+    // phase 1: everything that comes from DRAM, for all kUnroll indices
+    S x0[kUnroll], x1[kUnroll]; // the two values along the inner dimension of the long operand
     S old[kUnroll][2];
-    T *cp[kUnroll][2];
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
       const uint64_t t = t0 + u * step;
       if (t >= total) continue;
-      const uint64_t bt = t / g.len;
-      const uint64_t i = t - bt * g.len;
-      const T *a = static_cast<const T *>(g.a) + bt * g.stride_a;
-      const T *b = static_cast<const T *>(g.b) + bt * g.stride_b;
+      const uint64_t bt = t >> g.log2_len; // len is a power of two: no 64-bit division
+      const uint64_t i = t & (g.len - 1);
       T *c = static_cast<T *>(g.c) + bt * g.stride_c;
       if (LONG_IS_M) {
         // op(A)(i, l): stored A(i, l) = a[i + l*lda] or, transposed, a[l + i*lda]
+        const T *a = static_cast<const T *>(g.a) + bt * g.stride_a;
         x0[u] = load_val(g.trans_a ? a + i * g.lda : a + i, g.conj_a);
         x1[u] = load_val(g.trans_a ? a + 1 + i * g.lda : a + i + g.lda, g.conj_a);
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-          // op(B)(l, j): b[l + j*ldb] or, transposed, b[j + l*ldb]
-          q[u][2 * j] = load_val(g.trans_b ? b + j : b + j * g.ldb, g.conj_b);
-          q[u][2 * j + 1] = load_val(g.trans_b ? b + j + g.ldb : b + 1 + j * g.ldb, g.conj_b);
-          cp[u][j] = c + i + j * g.ldc;
-        }
       } else {
+        // op(B)(l, i): b[l + i*ldb] or, transposed, b[i + l*ldb]
+        const T *b = static_cast<const T *>(g.b) + bt * g.stride_b;
         x0[u] = load_val(g.trans_b ? b + i : b + i * g.ldb, g.conj_b);
         x1[u] = load_val(g.trans_b ? b + i + g.ldb : b + 1 + i * g.ldb, g.conj_b);
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-          q[u][2 * r] = load_val(g.trans_a ? a + r * g.lda : a + r, g.conj_a);
-          q[u][2 * r + 1] = load_val(g.trans_a ? a + 1 + r * g.lda : a + r + g.lda, g.conj_a);
-          cp[u][r] = c + r + i * g.ldc;
-        }
       }
-      if (g.read_c) {
-        old[u][0] = load_c(cp[u][0]);
-        old[u][1] = load_c(cp[u][1]);
-      } else {
-        old[u][0] = S{};
-        old[u][1] = S{};
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        old[u][j] = g.read_c ? load_c(LONG_IS_M ? c + i + j * g.ldc : c + j + i * g.ldc) : S{};
       }
     }
+    // phase 2: the 2 x 2 operand (a few cache-resident values per batch entry), arithmetic, stores
 #pragma unroll
     for (int u = 0; u < kUnroll; u++) {
-      if (t0 + u * step >= total) continue;
+      const uint64_t t = t0 + u * step;
+      if (t >= total) continue;
+      const uint64_t bt = t >> g.log2_len;
+      const uint64_t i = t & (g.len - 1);
+      T *c = static_cast<T *>(g.c) + bt * g.stride_c;
+      S q[4]; // q[2*j + l] = op(B)(l, j) resp. op(A)(j, l)
+      if (LONG_IS_M) {
+        const T *b = static_cast<const T *>(g.b) + bt * g.stride_b;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          q[2 * j] = load_val(g.trans_b ? b + j : b + j * g.ldb, g.conj_b);
+          q[2 * j + 1] = load_val(g.trans_b ? b + j + g.ldb : b + 1 + j * g.ldb, g.conj_b);
+        }
+      } else {
+        const T *a = static_cast<const T *>(g.a) + bt * g.stride_a;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          q[2 * r] = load_val(g.trans_a ? a + r * g.lda : a + r, g.conj_a);
+          q[2 * r + 1] = load_val(g.trans_a ? a + 1 + r * g.lda : a + r + g.lda, g.conj_a);
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 2; j++) {
         // the operand order inside each product is (value of A, value of B)
-        const S p = LONG_IS_M ? dot2(x0[u], q[u][2 * j], x1[u], q[u][2 * j + 1])
-                              : dot2(q[u][2 * j], x0[u], q[u][2 * j + 1], x1[u]);
-        store_result(cp[u][j], p, alpha, beta, old[u][j], g.read_c);
+        const S p = LONG_IS_M ? dot2(x0[u], q[2 * j], x1[u], q[2 * j + 1])
+                              : dot2(q[2 * j], x0[u], q[2 * j + 1], x1[u]);
+        store_result(LONG_IS_M ? c + i + j * g.ldc : c + j + i * g.ldc, p, alpha, beta,
+                     old[u][j], g.read_c);
       }
     }
   }
@@ -199,6 +206,8 @@ cublasStatus_t tiny_gemm(cuMpSGEMM_handle *h, bool long_is_m, cublasOperation_t 
   g.stride_b = stride_b;
   g.stride_c = stride_c;
   g.len = len;
+  g.log2_len = 0;
+  while ((1ull << g.log2_len) < len) ++g.log2_len;
   g.batch = batch;
   g.trans_a = op_A != CUBLAS_OP_N;
   g.conj_a = op_A == CUBLAS_OP_C;
