@@ -227,6 +227,138 @@ __global__ void __launch_bounds__(THREADS) max_only_kernel(const ScanParams s, f
   reduce_and_publish<false, true>(a, max_slot, nullptr, nullptr);
 }
 
+// ---------------------------------------------------------------- fused variants
+// exp_stats_ext / exp_max_ext outside the profiler use these: slot initialisation, scan and
+// decision in one launch per stage (two launches instead of five, one instead of two), which
+// is what an AUTO GEMM on a small matrix spends most of its time on otherwise.  Every CTA
+// writes its partial result to its own scratch record and takes a ticket; the CTA that draws
+// the last ticket adds the records up, writes the slot and takes the decision, then puts the
+// ticket counter back to zero for the next launch.  Sums of integers and a maximum do not
+// depend on the order, so the slot receives the same bits as on the five-launch path.
+struct ScanPartial {
+  unsigned long long total, underflow;
+  unsigned int max_bits, pad;
+};
+
+struct ScanTotals {
+  float max_abs;
+  unsigned long long total, underflow;
+};
+
+// Block-wide reduction of (max, total, underflow); the result is valid in thread 0.
+__device__ __forceinline__ ScanTotals block_reduce(ScanTotals a) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, off));
+    a.total += __shfl_xor_sync(0xffffffffu, a.total, off);
+    a.underflow += __shfl_xor_sync(0xffffffffu, a.underflow, off);
+  }
+  __shared__ float s_max[THREADS / 32];
+  __shared__ unsigned long long s_total[THREADS / 32];
+  __shared__ unsigned long long s_uf[THREADS / 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads(); // the arrays may still be read from an earlier call
+  if (lane == 0) {
+    s_max[warp] = a.max_abs;
+    s_total[warp] = a.total;
+    s_uf[warp] = a.underflow;
+  }
+  __syncthreads();
+  ScanTotals r{0.f, 0ull, 0ull};
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < THREADS / 32; ++w) {
+      r.max_abs = fmaxf(r.max_abs, s_max[w]);
+      r.total += s_total[w];
+      r.underflow += s_uf[w];
+    }
+  }
+  return r;
+}
+
+// Returns true in thread 0 of the CTA that drew the last ticket, with the grid-wide totals in
+// *out; false everywhere else.
+__device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsigned int *ticket,
+                                            ScanTotals *out) {
+  const ScanTotals mine = block_reduce(ScanTotals{acc.max_abs, acc.total, acc.underflow});
+  __shared__ bool s_last;
+  if (threadIdx.x == 0) {
+    ScanPartial rec;
+    rec.total = mine.total;
+    rec.underflow = mine.underflow;
+    rec.max_bits = __float_as_uint(mine.max_abs);
+    rec.pad = 0;
+    partials[blockIdx.x] = rec;
+    __threadfence();
+    s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return false;
+  __threadfence();
+  ScanTotals sum{0.f, 0ull, 0ull};
+  for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS) {
+    const volatile ScanPartial *r = partials + i;
+    sum.max_abs = fmaxf(sum.max_abs, __uint_as_float(r->max_bits));
+    sum.total += r->total;
+    sum.underflow += r->underflow;
+  }
+  *out = block_reduce(sum);
+  if (threadIdx.x == 0) *ticket = 0;
+  return threadIdx.x == 0;
+}
+
+__global__ void __launch_bounds__(THREADS)
+    fused_stage1_kernel(const ScanParams s, int *mode, float *max_slot,
+                        unsigned long long *total_slot, unsigned long long *uf_slot,
+                        float ignore_thr, float uf_thr, float tolerance, ScanPartial *partials,
+                        unsigned int *ticket) {
+  Acc a{0.f, 0u, 0u};
+  scan_items<true, true>(s, a, ignore_thr, uf_thr);
+  ScanTotals t;
+  if (!grid_reduce(a, partials, ticket, &t)) return;
+  // keep only the exponent field: 2^floor(log2 max|x|) as a float
+  const float mx = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
+  *max_slot = mx;
+  // the comparison is carried out in float, as in the reference
+  if ((static_cast<float>(t.underflow) > static_cast<float>(t.total) * tolerance) ||
+      (mx > 0.f && t.total == 0)) {
+    *mode = CUMPSGEMM_UNDEFINED;
+    *total_slot = 0;
+    *uf_slot = 0;
+  } else {
+    *mode = CUMPSGEMM_FP16TCEC;
+    *total_slot = t.total;
+    *uf_slot = t.underflow;
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+    fused_stage2_kernel(const ScanParams s, int *mode, const float *max_slot,
+                        unsigned long long *total_slot, unsigned long long *uf_slot,
+                        float half_ignore_thr, float half_uf_thr, float tolerance,
+                        ScanPartial *partials, unsigned int *ticket) {
+  if (*mode != CUMPSGEMM_UNDEFINED) return; // launch-and-exit, uniform over the grid
+  const float mx = *max_slot;
+  Acc a{0.f, 0u, 0u};
+  scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx);
+  ScanTotals t;
+  if (!grid_reduce(a, partials, ticket, &t)) return;
+  *total_slot = t.total;
+  *uf_slot = t.underflow;
+  *mode = (static_cast<float>(t.underflow) <= static_cast<float>(t.total) * tolerance)
+              ? CUMPSGEMM_FP16TCEC_SCALING
+              : CUMPSGEMM_TF32TCEC;
+}
+
+__global__ void __launch_bounds__(THREADS)
+    fused_max_only_kernel(const ScanParams s, float *max_slot, ScanPartial *partials,
+                          unsigned int *ticket) {
+  Acc a{0.f, 0u, 0u};
+  scan_items<false, true>(s, a, 0.f, 0.f);
+  ScanTotals t;
+  if (!grid_reduce(a, partials, ticket, &t)) return;
+  *max_slot = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
+}
+
 __global__ void configure_mode_buffer_kernel(int *mode_buffer) {
   mode_buffer[0] = CUMPSGEMM_TF32TCEC;
   mode_buffer[1] = CUMPSGEMM_FP16TCEC;
@@ -347,13 +479,48 @@ void exp_max_only(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, cons
   max_only_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(s, h->exp_stats.dev_max + id);
 }
 
+// One launch per stage (see the fused kernels above).
+inline ScanPartial *scan_partials(cuMpSGEMM_handle *h) {
+  return reinterpret_cast<ScanPartial *>(h->exp_stats.dev_scan_scratch);
+}
+inline unsigned int *scan_ticket(cuMpSGEMM_handle *h) {
+  return reinterpret_cast<unsigned int *>(scan_partials(h) + static_cast<size_t>(h->num_sms) * 8);
+}
+
+template <class T>
+void exp_stats_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
+                     unsigned ld, unsigned batch, unsigned stride) {
+  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
+  auto &es = h->exp_stats;
+  fused_stage1_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
+      s, es.dev_mode + id, es.dev_max + id, es.dev_total + id, es.dev_underflow + id,
+      es.ignore_threshold, es.underflow_threshold, es.underflow_tolerance_rate, scan_partials(h),
+      scan_ticket(h));
+  fused_stage2_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
+      s, es.dev_mode + id, es.dev_max + id, es.dev_total + id, es.dev_underflow + id,
+      es.ignore_threshold / 2, es.underflow_threshold / 2, es.underflow_tolerance_rate,
+      scan_partials(h), scan_ticket(h));
+}
+
+template <class T>
+void exp_max_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
+                   unsigned ld, unsigned batch, unsigned stride) {
+  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
+  fused_max_only_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
+      s, h->exp_stats.dev_max + id, scan_partials(h), scan_ticket(h));
+}
+
 #define INSTANTIATE(T)                                                                           \
   template void exp_stats_stage1<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *, \
                                     unsigned, unsigned, unsigned);                               \
   template void exp_stats_stage2<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *, \
                                     unsigned, unsigned, unsigned);                               \
   template void exp_max_only<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *,     \
-                                unsigned, unsigned, unsigned);
+                                unsigned, unsigned, unsigned);                                   \
+  template void exp_stats_fused<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *,  \
+                                   unsigned, unsigned, unsigned);                                \
+  template void exp_max_fused<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *,    \
+                                 unsigned, unsigned, unsigned);
 INSTANTIATE(float)
 INSTANTIATE(cuComplex)
 #undef INSTANTIATE
@@ -374,6 +541,11 @@ unsigned exp_stats_ext(cuMpSGEMM_handle_t handle, const unsigned m, const unsign
                        const unsigned stride) {
   DeviceGuard guard(handle->device);
   const unsigned id = next_exp_stats_id(handle);
+  if (!handle->exp_stats.profiling_enabled) {
+    // two launches; the five separate ones below exist for the named timers of the profiler
+    exp_stats_fused<T>(handle, id, m, n, ptr, ld, batch_size, stride);
+    return id;
+  }
   {
     ScopedTimer t(handle, "exp_stats_init");
     exp_stats_init_slot(handle, id);
@@ -409,7 +581,10 @@ unsigned exp_max_ext(cuMpSGEMM_handle_t handle, const unsigned m, const unsigned
                      const unsigned stride) {
   DeviceGuard guard(handle->device);
   const unsigned id = next_exp_stats_id(handle);
-  exp_max_only<T>(handle, id, m, n, ptr, ld, batch_size, stride);
+  if (!handle->exp_stats.profiling_enabled)
+    exp_max_fused<T>(handle, id, m, n, ptr, ld, batch_size, stride);
+  else
+    exp_max_only<T>(handle, id, m, n, ptr, ld, batch_size, stride);
   return id;
 }
 template unsigned exp_max_ext<float>(cuMpSGEMM_handle_t, const unsigned, const unsigned,

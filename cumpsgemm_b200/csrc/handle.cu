@@ -70,6 +70,8 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
         cudaSuccess;
   ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
   ok &= cudaMalloc(&h->dev_status, 2 * sizeof(int)) == cudaSuccess; // status, wave counter
+  const size_t scan_scratch_bytes = static_cast<size_t>(h->num_sms) * 8 * 24 + 16;
+  ok &= cudaMalloc(&es.dev_scan_scratch, scan_scratch_bytes) == cudaSuccess;
   if (!ok) {
     cuMpSGEMM_destroy(h);
     return CUBLAS_STATUS_ALLOC_FAILED;
@@ -82,6 +84,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
   cudaMemsetAsync(h->dyn_launch.flag_buffer, 0, sizeof(int) * h->dyn_launch.flag_buffer_length,
                   h->cuda_stream);
   cudaMemsetAsync(h->dev_status, 0, 2 * sizeof(int), h->cuda_stream);
+  cudaMemsetAsync(es.dev_scan_scratch, 0, scan_scratch_bytes, h->cuda_stream);
   configure_mode_buffer(h);
   init_flag_buffer(h);
   if (cudaStreamSynchronize(h->cuda_stream) != cudaSuccess) {
@@ -101,6 +104,7 @@ extern "C" cublasStatus_t cuMpSGEMM_destroy(cuMpSGEMM_handle_t handle) {
   cudaFree(handle->exp_stats.dev_underflow);
   cudaFree(handle->exp_stats.dev_max);
   cudaFree(handle->exp_stats.dev_mode);
+  cudaFree(handle->exp_stats.dev_scan_scratch);
   cudaFree(handle->dyn_launch.flag_buffer);
   cudaFree(handle->dev_dyn_params);
   cudaFree(handle->dev_status);

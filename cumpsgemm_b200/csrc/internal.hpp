@@ -78,6 +78,9 @@ struct ExpStatsState {
   std::uint32_t current_buffer_id = 1;
   Profiler profiler;
   bool profiling_enabled = false;
+  // Scratch of the one-launch-per-stage scans: one 24-byte record per CTA (num_sms * 8 of
+  // them) followed by the ticket counter, which every launch leaves at zero.
+  void *dev_scan_scratch = nullptr;
 };
 
 struct DynLaunchState {

@@ -54,6 +54,44 @@ def test_exp_stats_bit_exact_real(handle, oracle, case, params):
     assert handle.get_max_exp(mid) == oracle.exp_max(x, m, n, ld, batch, stride)
 
 
+@pytest.mark.parametrize("case", CASES)
+def test_one_launch_and_five_launch_paths_agree(handle, oracle, case):
+    """exp_stats_ext runs two fused launches normally and the reference's five separate steps
+    under the profiler (named timers): both leave the same slot, equal to the oracle's, for
+    every decision outcome; a large scan (many CTAs, every ticket drawn) is included."""
+    m, n, ld, batch, stride = case
+    count = (stride * batch if stride else ld * n) + 3
+    for seed, (lo, hi), params in ((1, (-3, 2), (0.0, 2.0 ** -15, 0.0)),
+                                   (2, (-24, -20), (0.0, 2.0 ** -15, 0.0)),
+                                   (3, (-30, 10), (0.0, 2.0 ** -15, 0.05))):
+        x = oracle.gen_wide_exponent(seed, count, lo=lo, hi=hi)
+        d = _dev(x)
+        handle.set_exp_stats_params(*params)
+        want = oracle.exp_stats(x, m, n, ld, batch, stride, *params)
+        fused = _slot(handle, handle.exp_stats_ext(m, n, d, ld, batch, stride))
+        fused_max = handle.get_max_exp(handle.exp_max_ext(m, n, d, ld, batch, stride))
+        handle.enable_exp_stats_profiling()
+        try:
+            stepwise = _slot(handle, handle.exp_stats_ext(m, n, d, ld, batch, stride))
+            stepwise_max = handle.get_max_exp(handle.exp_max_ext(m, n, d, ld, batch, stride))
+        finally:
+            handle.disable_exp_stats_profiling()
+        assert fused == want and stepwise == want
+        assert fused_max == stepwise_max == oracle.exp_max(x, m, n, ld, batch, stride)
+
+
+def test_fused_scan_on_a_large_matrix(handle, oracle):
+    m = n = 4096                       # 16 Mi values: more work items than resident CTAs
+    x = oracle.gen_wide_exponent(9, m * n, lo=-28, hi=4)
+    handle.set_exp_stats_params(0.0, 2.0 ** -15, 0.0)
+    d = _dev(x)
+    for _ in range(2):                 # the ticket counter is back at zero after every launch
+        sid = handle.exp_stats_ext(m, n, d, m)
+        assert _slot(handle, sid) == oracle.exp_stats(x, m, n, m, 1, 0, 0.0, 2.0 ** -15, 0.0)
+        mid = handle.exp_max_ext(m, n, d, m)
+        assert handle.get_max_exp(mid) == oracle.exp_max(x, m, n, m, 1, 0)
+
+
 def test_exp_stats_bit_exact_complex(handle, oracle):
     m, n, ld, batch, stride = 90, 40, 96, 3, 96 * 40
     cnt = stride * batch
