@@ -274,3 +274,47 @@ def test_pointer_array_batched_entry_points(oracle):
         assert buf.value.decode() == f"cublasCgemmBatched,N,N,{m},{n},{k},{batch},FP16TCEC"
     finally:
         lib.cuMpSGEMM_hijack_unset_compute_mode()
+
+
+TORCH_CLIENT = r"""
+import torch
+torch.backends.cuda.matmul.allow_tf32 = False
+g = torch.Generator(device="cuda"); g.manual_seed(5)
+a = torch.rand(1536, 1280, device="cuda", generator=g) * 2 - 1
+b = torch.rand(1280, 1152, device="cuda", generator=g) * 2 - 1
+c = a @ b                                   # 2-D FP32 matmul -> cuBLAS SGEMM
+z = torch.complex(a, a.flip(0)) @ torch.complex(b, b.flip(1))
+a2, b2 = torch.stack([a, a.flip(0)]), torch.stack([b, b.flip(1)])   # every size above 1024:
+bb = torch.bmm(a2, b2)                      # the default rule keeps smaller problems on cuBLAS
+torch.cuda.synchronize()
+def res(x, t): return float((x.double() - t).norm() / t.norm()) if not x.is_complex() else float((x.to(torch.complex128) - t).norm() / t.norm())
+print("RES_S", res(c, a.double() @ b.double()))
+print("RES_C", res(z, torch.complex(a, a.flip(0)).to(torch.complex128) @ torch.complex(b, b.flip(1)).to(torch.complex128)))
+print("RES_B", res(bb, torch.bmm(a2.double(), b2.double())))
+"""
+
+
+def test_pytorch_under_ld_preload():
+    """An unmodified PyTorch process: its FP32 / complex64 matmul and bmm reach cuBLAS through
+    the interposed symbols and come back with the corrected kernels' accuracy."""
+    _setup()
+    from cumpsgemm_b200 import build
+
+    env = dict(os.environ)
+    env.update({"LD_PRELOAD": str(build.library_path()), "CUMPSGEMM_COMPUTE_MODE": "FP16TCEC",
+                "CUMPSGEMM_INFO": "1"})
+    r = subprocess.run([sys.executable, "-c", TORCH_CLIENT], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    out = r.stdout
+    logs = LOG_RE.findall(out)
+    funcs = {entry[0] for entry in logs if entry[7] == "FP16TCEC"}
+    # which entry point PyTorch uses for each call is its own business; each of the three
+    # calls must have been intercepted and computed in the requested mode
+    assert len([entry for entry in logs if entry[7] == "FP16TCEC"]) >= 3, out[-3000:]
+    assert funcs <= {"cublasSgemm_v2", "cublasCgemm_v2", "cublasGemmEx", "cublasSgemmStridedBatched",
+                     "cublasCgemmStridedBatched", "cublasGemmStridedBatchedEx", "cublasSgemm_v2_64",
+                     "cublasGemmEx_64", "cublasSgemmBatched", "cublasGemmBatchedEx"}, funcs
+    for tag in ("RES_S", "RES_C", "RES_B"):
+        val = float(re.search(tag + r" (\S+)", out).group(1))
+        assert val < 2.0 ** -23 * np.sqrt(1280), (tag, val)
