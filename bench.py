@@ -330,7 +330,7 @@ def run_ours(args, rank, local_rank, world):
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                "steps": args.e2e_steps,
                "note": "per rank: api.HostGemm, A, B, C copied from pinned host memory and C "
-                       "copied back inside the timed region, pipelined over 8 column blocks; "
+                       "copied back inside the timed region, pipelined over 16 column blocks; "
                        "no NCCL broadcast on this leg"}
 
     cpu = None

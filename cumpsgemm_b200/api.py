@@ -432,7 +432,7 @@ class HostGemm:
     C_host once that stream reaches it.
     """
 
-    def __init__(self, handle: Handle, device=None, column_blocks: int = 8):
+    def __init__(self, handle: Handle, device=None, column_blocks: int = 16):
         import torch
 
         self.handle = handle
