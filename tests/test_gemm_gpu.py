@@ -209,6 +209,49 @@ def test_strided_batch_sgemm_and_cgemm(handle, oracle):
         assert oracle.residual(truth, zres[i * m * n:(i + 1) * m * n], m) < oracle.error_threshold(True, k)
 
 
+@pytest.mark.parametrize("mode", [FP16TCEC, TF32TCEC])
+def test_pair_kernel_ragged_multiwave_batched(handle, oracle, mode):
+    """The persistent CTA-pair kernel where all of its scheduling features are active at once:
+    more tiles than cluster slots (several waves, paced), a K loop long enough for the longer
+    first drain chunk, m / n / k that are not multiples of the tile, padded leading dimensions,
+    beta != 0, a batch of two, and the same for complex operands."""
+    torch = _torch()
+    batch, m, n, k = 4, 612, 2381, 2088          # 3 x 10 pair tiles per entry: 120 on 74 slots
+    os.environ["CUMPSGEMM_TILE_N"] = "256"       # force the pair kernel whatever the tile rule says
+    os.environ["CUMPSGEMM_PAIR"] = "1"
+    try:
+        lda, ldb, ldc = m + 4, k + 8, m + 12
+        sa, sb, sc = lda * k + 16, ldb * n + 4, ldc * n
+        a = oracle.gen_uniform_exp(21, sa * batch, -4, 4)
+        b = oracle.gen_uniform_exp(22, sb * batch, -4, 4)
+        c0 = oracle.gen_uniform(23, sc * batch)
+        da, db, dc = _dev(a), _dev(b), _dev(c0.copy())
+        handle.gemm_strided_batch(N, N, m, n, k, 1.5, da, lda, sa, db, ldb, sb, -0.5, dc, ldc, sc,
+                                  batch, mode)
+        res = dc.cpu().numpy()
+        for i in range(batch):
+            truth = oracle.gemm_f64(N, N, m, n, k, 1.5, a[i * sa:], lda, b[i * sb:], ldb, -0.5,
+                                    c0[i * sc:], ldc)
+            assert oracle.residual(truth, res[i * sc:(i + 1) * sc], ldc) < oracle.error_threshold(True, k)
+            # rows of C beyond m (padding of the leading dimension) are untouched
+            pad_got = res[i * sc:(i + 1) * sc].reshape(n, ldc)[:, m:]
+            pad_was = c0[i * sc:(i + 1) * sc].reshape(n, ldc)[:, m:]
+            assert np.array_equal(pad_got, pad_was)
+        # complex, transposed / conjugated operands
+        mz, nz, kz = 330, 2330, 1100
+        za = (oracle.gen_uniform(31, kz * mz) + 1j * oracle.gen_uniform(32, kz * mz)).astype(np.complex64)
+        zb = (oracle.gen_uniform(33, nz * kz) + 1j * oracle.gen_uniform(34, nz * kz)).astype(np.complex64)
+        zc0 = (oracle.gen_uniform(35, mz * nz) + 1j * oracle.gen_uniform(36, mz * nz)).astype(np.complex64)
+        dza, dzb, dzc = _dev(za), _dev(zb), _dev(zc0.copy())
+        handle.gemm(Cj, T, mz, nz, kz, 1.0 - 0.5j, dza, kz, dzb, nz, 0.25 + 0.5j, dzc, mz, mode)
+        truth = oracle.gemm_f64(Cj, T, mz, nz, kz, 1.0 - 0.5j, za, kz, zb, nz, 0.25 + 0.5j, zc0, mz)
+        assert oracle.residual(truth, dzc.cpu().numpy(), mz) < oracle.error_threshold(True, kz)
+        assert handle.kernel_status() == 0
+    finally:
+        os.environ.pop("CUMPSGEMM_TILE_N", None)
+        os.environ.pop("CUMPSGEMM_PAIR", None)
+
+
 def test_beta_zero_ignores_nan_in_c(handle, oracle):
     torch = _torch()
     m = n = k = 128
