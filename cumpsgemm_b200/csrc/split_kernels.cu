@@ -85,32 +85,46 @@ __device__ __forceinline__ void split_generic_body(const SplitParams &p, const u
                          : p.src + static_cast<uint64_t>(b) * p.stride * ES;
 
   // ---- phase 1: coalesced read along the source-contiguous dimension
-  for (int idx = threadIdx.x; idx < SR * SK; idx += THREADS) {
-    int r, kk;
-    if (p.src_k_contig) {
-      kk = idx % SK;
-      r = idx / SK;
-    } else {
-      r = idx % SR;
-      kk = idx / SR;
+  if constexpr (ES == 2) {
+    // Complex: a thread's 4 (A') or 8 (B') loads are all issued before the first
+    // shared-memory store; with one load per store the kernel spent over half of its warp
+    // cycles waiting for the load just issued.
+    constexpr int PER = SR * SK / THREADS;
+    float2 v[PER];
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+      const int idx = threadIdx.x + q * THREADS;
+      const int r = p.src_k_contig ? idx / SK : idx % SR;
+      const int kk = p.src_k_contig ? idx % SK : idx / SR;
+      const uint64_t gr = r0 + r, gk = k0 + kk;
+      v[q] = make_float2(0.f, 0.f);
+      if (gr < p.rows && gk < p.k)
+        v[q] = reinterpret_cast<const float2 *>(src)[p.src_k_contig ? (gk + gr * p.ld)
+                                                                    : (gr + gk * p.ld)];
     }
-    const uint64_t gr = r0 + r, gk = k0 + kk;
-    float re = 0.f, im = 0.f;
-    if (gr < p.rows && gk < p.k) {
-      const uint64_t off = p.src_k_contig ? (gk + gr * p.ld) : (gr + gk * p.ld);
-      if constexpr (ES == 1) {
-        re = src[off] * scale;
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+      const int idx = threadIdx.x + q * THREADS;
+      const int r = p.src_k_contig ? idx / SK : idx % SR;
+      const int kk = p.src_k_contig ? idx % SK : idx / SR;
+      tile[r][2 * kk] = v[q].x * scale;
+      tile[r][2 * kk + 1] = (p.conj ? -v[q].y : v[q].y) * scale;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < SR * SK; idx += THREADS) {
+      int r, kk;
+      if (p.src_k_contig) {
+        kk = idx % SK;
+        r = idx / SK;
       } else {
-        const float2 v = reinterpret_cast<const float2 *>(src)[off];
-        re = v.x * scale;
-        im = (p.conj ? -v.y : v.y) * scale;
+        r = idx % SR;
+        kk = idx / SR;
       }
-    }
-    if constexpr (ES == 1) {
+      const uint64_t gr = r0 + r, gk = k0 + kk;
+      float re = 0.f;
+      if (gr < p.rows && gk < p.k)
+        re = src[p.src_k_contig ? (gk + gr * p.ld) : (gr + gk * p.ld)] * scale;
       tile[r][kk] = re;
-    } else {
-      tile[r][2 * kk] = re;
-      tile[r][2 * kk + 1] = im;
     }
   }
   __syncthreads();
