@@ -47,8 +47,9 @@ METRIC = "effective TFLOP/s of FP16TCEC SGEMM at N=16384"
 UNIT = "TFLOP/s"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM-kernel launch, from the one-pass ncu
-# capture summarised in profiles/tcec_gemm_pair_kernel_fp16tcec.md; keyed by (mode, m, n, k).
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM-kernel launch, from a one-pass ncu
+# capture of this script (--steps 1 --warmup 1, kernel filter tcec_gemm_pair); keyed by
+# (mode, m, n, k).
 # Algorithmic minimum for the same launch: panels 2 x 1 GiB + C read 1 GiB + C written 1 GiB.
 MEASURED_DRAM_BYTES = {("FP16TCEC", 16384, 16384, 16384): 22.97e9 + 1.16e9}
 
