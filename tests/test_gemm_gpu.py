@@ -400,6 +400,73 @@ def test_calls_replay_from_a_cuda_graph(oracle):
     h.destroy()
 
 
+def test_two_handles_on_two_streams_at_once(oracle):
+    """Two persistent GEMM kernels that share the GPU: the clusters of the second are not all
+    resident while the first runs, so its pacing waits run out (and pacing switches itself off
+    for that launch).  That may cost time, never correctness: both results equal the ones
+    computed alone, bit for bit, and no bounded wait of the pipeline itself expires."""
+    torch = _torch()
+    from cumpsgemm_b200 import api
+
+    m, n, k = 3072, 4096, 2304                    # 192 pair tiles, 36 K stages: paced
+    g = torch.Generator(device="cuda")
+    g.manual_seed(17)
+    ops = []
+    for _ in range(2):
+        a = torch.rand(m * k, device="cuda", generator=g) * 2 - 1
+        b = torch.rand(k * n, device="cuda", generator=g) * 2 - 1
+        ops.append((a, b, torch.zeros(m * n, device="cuda"), torch.zeros(m * n, device="cuda")))
+    handles = [api.Handle(), api.Handle()]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    # alone, one after the other
+    for h, s, (a, b, c_alone, _) in zip(handles, streams, ops):
+        with torch.cuda.stream(s):
+            h.use_current_torch_stream()
+            h.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c_alone, m, FP16TCEC)
+        s.synchronize()
+    # together, several rounds so that the launches really overlap
+    for _ in range(4):
+        for h, s, (a, b, _, c_both) in zip(handles, streams, ops):
+            with torch.cuda.stream(s):
+                h.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c_both, m, FP16TCEC)
+    torch.cuda.synchronize()
+    for h, (a, b, c_alone, c_both) in zip(handles, ops):
+        assert torch.equal(c_alone, c_both)
+        assert h.kernel_status() == 0
+    ah, bh, ch = (x.cpu().numpy() for x in ops[1][:3])
+    truth = oracle.gemm_f64(N, N, m, 1, k, 1.0, ah, m, bh[5 * k:], k, 0.0, None, m)
+    assert oracle.residual(truth, ch[5 * m:6 * m], m) < oracle.error_threshold(True, k)
+    for h in handles:
+        h.destroy()
+
+
+def test_handles_can_be_created_and_destroyed_repeatedly():
+    """Create / use / destroy in a loop leaves device memory where it was (workspace, ring
+    buffers and scratch are freed; reference leak: src/handle.cu:40-46)."""
+    torch = _torch()
+    from cumpsgemm_b200 import api
+
+    x = torch.rand(512 * 512, device="cuda")
+    y = torch.zeros(512 * 512, device="cuda")
+    torch.cuda.synchronize()
+
+    def cycle():
+        h = api.Handle()
+        h.use_current_torch_stream()
+        h.gemm(N, N, 512, 512, 512, 1.0, x, 512, x, 512, 0.0, y, 512, FP16TCEC)
+        h.exp_stats_ext(512, 512, x, 512)
+        torch.cuda.synchronize()
+        h.destroy()
+
+    cycle()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(20):
+        cycle()
+    free_after = torch.cuda.mem_get_info()[0]
+    assert free_before - free_after < (8 << 20), (free_before, free_after)
+
+
 def test_host_buffer_gemm_pipelined_matches_resident(handle, oracle):
     """api.HostGemm (pinned host operands, column-block pipeline) against the resident call."""
     from cumpsgemm_b200 import api
