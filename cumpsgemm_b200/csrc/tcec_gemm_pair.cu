@@ -13,6 +13,12 @@
 // ahead into the next tile while the epilogue warps still write the previous one: the next
 // tile's operands are loaded and its hi*hi products start as soon as the last drain of D0 is
 // done; its correction products wait only until the epilogue has copied D1 into registers.
+// Three schedule details came out of measurements and are explained where they are coded:
+// clusters announce every tile start on a device counter and wait for their wave (keeps
+// clusters that share panel rows at the same k, so the rows are fetched from DRAM once per
+// wave); the first drain chunk of a tile is longer than the others (the epilogue warps are
+// still storing the previous tile then); with beta != 0 the C tile is prefetched into L2 and
+// read in groups of columns.
 //
 // Barriers (one set per CTA at identical shared-memory offsets; "leader" = cluster rank 0):
 //   full[s]   leader's only: 1 arrival (leader's producer, expect_tx of both CTAs' bytes);
