@@ -306,7 +306,7 @@ __device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsi
   return threadIdx.x == 0;
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 8)
     fused_stage1_kernel(const ScanParams s, int *mode, float *max_slot,
                         unsigned long long *total_slot, unsigned long long *uf_slot,
                         float ignore_thr, float uf_thr, float tolerance, ScanPartial *partials,
@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(THREADS)
   }
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 8)
     fused_stage2_kernel(const ScanParams s, int *mode, const float *max_slot,
                         unsigned long long *total_slot, unsigned long long *uf_slot,
                         float half_ignore_thr, float half_uf_thr, float tolerance,
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(THREADS)
               : CUMPSGEMM_TF32TCEC;
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 8)
     fused_max_only_kernel(const ScanParams s, float *max_slot, ScanPartial *partials,
                           unsigned int *ticket) {
   Acc a{0.f, 0u, 0u};
