@@ -142,6 +142,30 @@ __global__ void dyn_params_kernel(DynParams *out, const int *flag, const float *
   out->gemm_mode = (mode == CUMPSGEMM_TF32TCEC) ? CUMPSGEMM_TF32TCEC : CUMPSGEMM_FP16TCEC;
 }
 
+// flag_from_stats_kernel and dyn_params_kernel in one launch (the AUTO path of a GEMM call).
+__global__ void flag_and_dyn_params_kernel(DynParams *out, int *flag, const int *mode_a,
+                                           const int *mode_b, const float *max_a,
+                                           const float *max_b) {
+  const int pa = *mode_a, pb = *mode_b;
+  int f;
+  if (pa == CUMPSGEMM_TF32TCEC || pb == CUMPSGEMM_TF32TCEC) {
+    f = CUMPSGEMM_TF32TCEC;
+  } else {
+    f = CUMPSGEMM_FP16TCEC;
+    if (pa == CUMPSGEMM_FP16TCEC_SCALING) f |= kFlagScaleA;
+    if (pb == CUMPSGEMM_FP16TCEC_SCALING) f |= kFlagScaleB;
+  }
+  *flag = f;
+  const float ma = *max_a, mb = *max_b;
+  const bool sa = flag_scale_a(f) && ma != 0.f;
+  const bool sb = flag_scale_b(f) && mb != 0.f;
+  out->scale_a = sa ? kHalfExpMax / ma : 1.f;
+  out->scale_b = sb ? kHalfExpMax / mb : 1.f;
+  out->unscale_c = (sa ? ma / kHalfExpMax : 1.f) * (sb ? mb / kHalfExpMax : 1.f);
+  const int mode = flag_gemm_mode(f);
+  out->gemm_mode = (mode == CUMPSGEMM_TF32TCEC) ? CUMPSGEMM_TF32TCEC : CUMPSGEMM_FP16TCEC;
+}
+
 unsigned scale_grid(const cuMpSGEMM_handle *h, const ScaleParams &s) {
   const uint64_t cap = static_cast<uint64_t>(h->num_sms) * 8;
   return static_cast<unsigned>(s.items < cap ? (s.items ? s.items : 1) : cap);
@@ -204,6 +228,17 @@ DynParams *prepare_dyn_params(cuMpSGEMM_handle *h, unsigned flag_id, unsigned st
   dyn_params_kernel<<<1, 1, 0, h->cuda_stream>>>(slot, h->dyn_launch.flag_buffer + flag_id,
                                                  h->exp_stats.dev_max + stats_id_a,
                                                  h->exp_stats.dev_max + stats_id_b);
+  return slot;
+}
+
+DynParams *prepare_dyn_params_from_stats(cuMpSGEMM_handle *h, unsigned flag_id,
+                                         unsigned stats_id_a, unsigned stats_id_b) {
+  DynParams *slot = h->dev_dyn_params + h->dyn_params_next;
+  h->dyn_params_next = (h->dyn_params_next + 1) % h->dyn_params_length;
+  flag_and_dyn_params_kernel<<<1, 1, 0, h->cuda_stream>>>(
+      slot, h->dyn_launch.flag_buffer + flag_id, h->exp_stats.dev_mode + stats_id_a,
+      h->exp_stats.dev_mode + stats_id_b, h->exp_stats.dev_max + stats_id_a,
+      h->exp_stats.dev_max + stats_id_b);
   return slot;
 }
 

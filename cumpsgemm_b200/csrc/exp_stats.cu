@@ -82,10 +82,13 @@ __device__ __forceinline__ void visit(float x, Acc &a, float ignore_thr, float u
   }
 }
 
+// `bid` of `nblocks` CTAs share the work items of one operand (a launch may serve two operands,
+// each with its own range of CTAs).
 template <bool COUNT, bool MAXV>
 __device__ __forceinline__ void scan_items(const ScanParams &s, Acc &a, float ignore_thr,
-                                           float uf_thr) {
-  for (uint64_t item = blockIdx.x; item < s.items; item += gridDim.x) {
+                                           float uf_thr, unsigned int bid = blockIdx.x,
+                                           unsigned int nblocks = gridDim.x) {
+  for (uint64_t item = bid; item < s.items; item += nblocks) {
     const uint64_t chunk = item % s.chunks_per_col;
     const uint64_t col_id = item / s.chunks_per_col;
     const uint64_t col = col_id % s.n;
@@ -278,7 +281,8 @@ __device__ __forceinline__ ScanTotals block_reduce(ScanTotals a) {
 // Returns true in thread 0 of the CTA that drew the last ticket, with the grid-wide totals in
 // *out; false everywhere else.
 __device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsigned int *ticket,
-                                            ScanTotals *out) {
+                                            ScanTotals *out, unsigned int bid = blockIdx.x,
+                                            unsigned int nblocks = gridDim.x) {
   const ScanTotals mine = block_reduce(ScanTotals{acc.max_abs, acc.total, acc.underflow});
   __shared__ bool s_last;
   if (threadIdx.x == 0) {
@@ -287,15 +291,15 @@ __device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsi
     rec.underflow = mine.underflow;
     rec.max_bits = __float_as_uint(mine.max_abs);
     rec.pad = 0;
-    partials[blockIdx.x] = rec;
+    partials[bid] = rec;
     __threadfence();
-    s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1);
+    s_last = (atomicAdd(ticket, 1u) == nblocks - 1);
   }
   __syncthreads();
   if (!s_last) return false;
   __threadfence();
   ScanTotals sum{0.f, 0ull, 0ull};
-  for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS) {
+  for (unsigned int i = threadIdx.x; i < nblocks; i += THREADS) {
     const volatile ScanPartial *r = partials + i;
     sum.max_abs = fmaxf(sum.max_abs, __uint_as_float(r->max_bits));
     sum.total += r->total;
@@ -306,57 +310,121 @@ __device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsi
   return threadIdx.x == 0;
 }
 
-__global__ void __launch_bounds__(THREADS, 8)
-    fused_stage1_kernel(const ScanParams s, int *mode, float *max_slot,
-                        unsigned long long *total_slot, unsigned long long *uf_slot,
-                        float ignore_thr, float uf_thr, float tolerance, ScanPartial *partials,
-                        unsigned int *ticket) {
+// Where one operand's results go.
+struct StatSlots {
+  int *mode;
+  float *max_slot;
+  unsigned long long *total_slot, *uf_slot;
+};
+
+__device__ __forceinline__ void fused_stage1_body(const ScanParams &s, const StatSlots &o,
+                                                  float ignore_thr, float uf_thr, float tolerance,
+                                                  ScanPartial *partials, unsigned int *ticket,
+                                                  unsigned int bid, unsigned int nblocks) {
   Acc a{0.f, 0u, 0u};
-  scan_items<true, true>(s, a, ignore_thr, uf_thr);
+  scan_items<true, true>(s, a, ignore_thr, uf_thr, bid, nblocks);
   ScanTotals t;
-  if (!grid_reduce(a, partials, ticket, &t)) return;
+  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks)) return;
   // keep only the exponent field: 2^floor(log2 max|x|) as a float
   const float mx = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
-  *max_slot = mx;
+  *o.max_slot = mx;
   // the comparison is carried out in float, as in the reference
   if ((static_cast<float>(t.underflow) > static_cast<float>(t.total) * tolerance) ||
       (mx > 0.f && t.total == 0)) {
-    *mode = CUMPSGEMM_UNDEFINED;
-    *total_slot = 0;
-    *uf_slot = 0;
+    *o.mode = CUMPSGEMM_UNDEFINED;
+    *o.total_slot = 0;
+    *o.uf_slot = 0;
   } else {
-    *mode = CUMPSGEMM_FP16TCEC;
-    *total_slot = t.total;
-    *uf_slot = t.underflow;
+    *o.mode = CUMPSGEMM_FP16TCEC;
+    *o.total_slot = t.total;
+    *o.uf_slot = t.underflow;
   }
 }
 
-__global__ void __launch_bounds__(THREADS, 8)
-    fused_stage2_kernel(const ScanParams s, int *mode, const float *max_slot,
-                        unsigned long long *total_slot, unsigned long long *uf_slot,
-                        float half_ignore_thr, float half_uf_thr, float tolerance,
-                        ScanPartial *partials, unsigned int *ticket) {
-  if (*mode != CUMPSGEMM_UNDEFINED) return; // launch-and-exit, uniform over the grid
-  const float mx = *max_slot;
+__device__ __forceinline__ void fused_stage2_body(const ScanParams &s, const StatSlots &o,
+                                                  float half_ignore_thr, float half_uf_thr,
+                                                  float tolerance, ScanPartial *partials,
+                                                  unsigned int *ticket, unsigned int bid,
+                                                  unsigned int nblocks) {
+  if (*o.mode != CUMPSGEMM_UNDEFINED) return; // launch-and-exit, uniform over the operand's CTAs
+  const float mx = *o.max_slot;
   Acc a{0.f, 0u, 0u};
-  scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx);
+  scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx, bid, nblocks);
   ScanTotals t;
-  if (!grid_reduce(a, partials, ticket, &t)) return;
-  *total_slot = t.total;
-  *uf_slot = t.underflow;
-  *mode = (static_cast<float>(t.underflow) <= static_cast<float>(t.total) * tolerance)
-              ? CUMPSGEMM_FP16TCEC_SCALING
-              : CUMPSGEMM_TF32TCEC;
+  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks)) return;
+  *o.total_slot = t.total;
+  *o.uf_slot = t.underflow;
+  *o.mode = (static_cast<float>(t.underflow) <= static_cast<float>(t.total) * tolerance)
+                ? CUMPSGEMM_FP16TCEC_SCALING
+                : CUMPSGEMM_TF32TCEC;
+}
+
+__device__ __forceinline__ void fused_max_body(const ScanParams &s, float *max_slot,
+                                               ScanPartial *partials, unsigned int *ticket,
+                                               unsigned int bid, unsigned int nblocks) {
+  Acc a{0.f, 0u, 0u};
+  scan_items<false, true>(s, a, 0.f, 0.f, bid, nblocks);
+  ScanTotals t;
+  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks)) return;
+  *max_slot = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
+}
+
+__global__ void __launch_bounds__(THREADS, 8)
+    fused_stage1_kernel(const ScanParams s, const StatSlots o, float ignore_thr, float uf_thr,
+                        float tolerance, ScanPartial *partials, unsigned int *ticket) {
+  fused_stage1_body(s, o, ignore_thr, uf_thr, tolerance, partials, ticket, blockIdx.x, gridDim.x);
+}
+
+__global__ void __launch_bounds__(THREADS, 8)
+    fused_stage2_kernel(const ScanParams s, const StatSlots o, float half_ignore_thr,
+                        float half_uf_thr, float tolerance, ScanPartial *partials,
+                        unsigned int *ticket) {
+  fused_stage2_body(s, o, half_ignore_thr, half_uf_thr, tolerance, partials, ticket, blockIdx.x,
+                    gridDim.x);
 }
 
 __global__ void __launch_bounds__(THREADS, 8)
     fused_max_only_kernel(const ScanParams s, float *max_slot, ScanPartial *partials,
                           unsigned int *ticket) {
-  Acc a{0.f, 0u, 0u};
-  scan_items<false, true>(s, a, 0.f, 0.f);
-  ScanTotals t;
-  if (!grid_reduce(a, partials, ticket, &t)) return;
-  *max_slot = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
+  fused_max_body(s, max_slot, partials, ticket, blockIdx.x, gridDim.x);
+}
+
+// Two operands in one launch (the A and B of a GEMM): CTAs [0, grid_a) scan the first, the
+// rest the second; each operand has its own records (second half of `partials`) and ticket.
+struct DualScan {
+  ScanParams s[2];
+  StatSlots o[2];
+  unsigned int grid_a;
+  unsigned int records_per_operand;
+};
+
+__global__ void __launch_bounds__(THREADS, 8)
+    fused_stage1_dual_kernel(const DualScan d, float ignore_thr, float uf_thr, float tolerance,
+                             ScanPartial *partials, unsigned int *tickets) {
+  const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
+  const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
+  const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
+  fused_stage1_body(d.s[w], d.o[w], ignore_thr, uf_thr, tolerance,
+                    partials + w * d.records_per_operand, tickets + w, bid, nb);
+}
+
+__global__ void __launch_bounds__(THREADS, 8)
+    fused_stage2_dual_kernel(const DualScan d, float half_ignore_thr, float half_uf_thr,
+                             float tolerance, ScanPartial *partials, unsigned int *tickets) {
+  const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
+  const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
+  const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
+  fused_stage2_body(d.s[w], d.o[w], half_ignore_thr, half_uf_thr, tolerance,
+                    partials + w * d.records_per_operand, tickets + w, bid, nb);
+}
+
+__global__ void __launch_bounds__(THREADS, 8)
+    fused_max_dual_kernel(const DualScan d, ScanPartial *partials, unsigned int *tickets) {
+  const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
+  const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
+  const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
+  fused_max_body(d.s[w], d.o[w].max_slot, partials + w * d.records_per_operand, tickets + w, bid,
+                 nb);
 }
 
 __global__ void configure_mode_buffer_kernel(int *mode_buffer) {
@@ -479,12 +547,18 @@ void exp_max_only(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, cons
   max_only_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(s, h->exp_stats.dev_max + id);
 }
 
-// One launch per stage (see the fused kernels above).
+// One launch per stage (see the fused kernels above).  Scratch layout: two operands' records
+// (num_sms * 8 each), then two tickets.
+inline unsigned int scan_records(const cuMpSGEMM_handle *h) { return h->num_sms * 8u; }
 inline ScanPartial *scan_partials(cuMpSGEMM_handle *h) {
   return reinterpret_cast<ScanPartial *>(h->exp_stats.dev_scan_scratch);
 }
-inline unsigned int *scan_ticket(cuMpSGEMM_handle *h) {
-  return reinterpret_cast<unsigned int *>(scan_partials(h) + static_cast<size_t>(h->num_sms) * 8);
+inline unsigned int *scan_tickets(cuMpSGEMM_handle *h) {
+  return reinterpret_cast<unsigned int *>(scan_partials(h) + 2u * scan_records(h));
+}
+inline StatSlots stat_slots(cuMpSGEMM_handle *h, unsigned id) {
+  auto &es = h->exp_stats;
+  return StatSlots{es.dev_mode + id, es.dev_max + id, es.dev_total + id, es.dev_underflow + id};
 }
 
 template <class T>
@@ -493,13 +567,11 @@ void exp_stats_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, c
   const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
   auto &es = h->exp_stats;
   fused_stage1_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
-      s, es.dev_mode + id, es.dev_max + id, es.dev_total + id, es.dev_underflow + id,
-      es.ignore_threshold, es.underflow_threshold, es.underflow_tolerance_rate, scan_partials(h),
-      scan_ticket(h));
+      s, stat_slots(h, id), es.ignore_threshold, es.underflow_threshold,
+      es.underflow_tolerance_rate, scan_partials(h), scan_tickets(h));
   fused_stage2_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
-      s, es.dev_mode + id, es.dev_max + id, es.dev_total + id, es.dev_underflow + id,
-      es.ignore_threshold / 2, es.underflow_threshold / 2, es.underflow_tolerance_rate,
-      scan_partials(h), scan_ticket(h));
+      s, stat_slots(h, id), es.ignore_threshold / 2, es.underflow_threshold / 2,
+      es.underflow_tolerance_rate, scan_partials(h), scan_tickets(h));
 }
 
 template <class T>
@@ -507,7 +579,35 @@ void exp_max_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, con
                    unsigned ld, unsigned batch, unsigned stride) {
   const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
   fused_max_only_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
-      s, h->exp_stats.dev_max + id, scan_partials(h), scan_ticket(h));
+      s, h->exp_stats.dev_max + id, scan_partials(h), scan_tickets(h));
+}
+
+// Statistics (full = true) or maximum exponent only of the two operands of a GEMM, two slots,
+// in two launches resp. one.  Same slot contents as two separate calls.
+template <class T>
+void exp_stats_pair(cuMpSGEMM_handle *h, bool full, unsigned id_a, unsigned am, unsigned an,
+                    const T *a, unsigned lda, unsigned stride_a, unsigned id_b, unsigned bm,
+                    unsigned bn, const T *b, unsigned ldb, unsigned stride_b, unsigned batch) {
+  DualScan d;
+  d.s[0] = make_scan(a, am, an, lda, batch, stride_a, floats_per_elem<T>());
+  d.s[1] = make_scan(b, bm, bn, ldb, batch, stride_b, floats_per_elem<T>());
+  d.o[0] = stat_slots(h, id_a);
+  d.o[1] = stat_slots(h, id_b);
+  d.grid_a = scan_grid(h, d.s[0]);
+  d.records_per_operand = scan_records(h);
+  const unsigned grid = d.grid_a + scan_grid(h, d.s[1]);
+  auto &es = h->exp_stats;
+  if (!full) {
+    fused_max_dual_kernel<<<grid, THREADS, 0, h->cuda_stream>>>(d, scan_partials(h),
+                                                                scan_tickets(h));
+    return;
+  }
+  fused_stage1_dual_kernel<<<grid, THREADS, 0, h->cuda_stream>>>(
+      d, es.ignore_threshold, es.underflow_threshold, es.underflow_tolerance_rate,
+      scan_partials(h), scan_tickets(h));
+  fused_stage2_dual_kernel<<<grid, THREADS, 0, h->cuda_stream>>>(
+      d, es.ignore_threshold / 2, es.underflow_threshold / 2, es.underflow_tolerance_rate,
+      scan_partials(h), scan_tickets(h));
 }
 
 #define INSTANTIATE(T)                                                                           \
@@ -520,7 +620,10 @@ void exp_max_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, con
   template void exp_stats_fused<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *,  \
                                    unsigned, unsigned, unsigned);                                \
   template void exp_max_fused<T>(cuMpSGEMM_handle *, unsigned, unsigned, unsigned, const T *,    \
-                                 unsigned, unsigned, unsigned);
+                                 unsigned, unsigned, unsigned);                                  \
+  template void exp_stats_pair<T>(cuMpSGEMM_handle *, bool, unsigned, unsigned, unsigned,        \
+                                  const T *, unsigned, unsigned, unsigned, unsigned, unsigned,   \
+                                  const T *, unsigned, unsigned, unsigned);
 INSTANTIATE(float)
 INSTANTIATE(cuComplex)
 #undef INSTANTIATE

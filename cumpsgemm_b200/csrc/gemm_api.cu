@@ -298,26 +298,40 @@ cublasStatus_t gemm_with_statistics(cuMpSGEMM_handle *h, cublasOperation_t op_A,
   const unsigned sb = batch > 1 ? static_cast<unsigned>(strideb) : 0u;
   unsigned id_a, id_b, flag_id;
   cuMpSGEMM_compute_mode_t gemm_mode;
+  const DynParams *dyn;
+  const bool fused_scans = !h->exp_stats.profiling_enabled;
+  if (fused_scans) {
+    // both operands share the scan launches; the slot ids are taken in the usual order
+    id_a = next_exp_stats_id(h);
+    id_b = next_exp_stats_id(h);
+    exp_stats_pair<T>(h, mode == CUMPSGEMM_AUTO, id_a, am, an, a, static_cast<unsigned>(lda), sa,
+                      id_b, bm, bn, b, static_cast<unsigned>(ldb), sb,
+                      static_cast<unsigned>(batch));
+  }
   if (mode == CUMPSGEMM_AUTO) {
-    id_a = cumpsgemm::exp_stats_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
-                                       static_cast<unsigned>(batch), sa);
-    id_b = cumpsgemm::exp_stats_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
-                                       static_cast<unsigned>(batch), sb);
+    if (!fused_scans) {
+      id_a = cumpsgemm::exp_stats_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
+                                         static_cast<unsigned>(batch), sa);
+      id_b = cumpsgemm::exp_stats_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
+                                         static_cast<unsigned>(batch), sb);
+    }
     flag_id = next_dyn_launch_id(h);
-    cumpsgemm::set_dynamic_launch_buffer_by_exp_stats(h, flag_id, id_a, id_b);
+    dyn = prepare_dyn_params_from_stats(h, flag_id, id_a, id_b);
     gemm_mode = CUMPSGEMM_AUTO;
   } else {
-    id_a = cumpsgemm::exp_max_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
-                                     static_cast<unsigned>(batch), sa);
-    id_b = cumpsgemm::exp_max_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
-                                     static_cast<unsigned>(batch), sb);
+    if (!fused_scans) {
+      id_a = cumpsgemm::exp_max_ext<T>(h, am, an, a, static_cast<unsigned>(lda),
+                                       static_cast<unsigned>(batch), sa);
+      id_b = cumpsgemm::exp_max_ext<T>(h, bm, bn, b, static_cast<unsigned>(ldb),
+                                       static_cast<unsigned>(batch), sb);
+    }
     flag_id = 1; // reserved slot: FP16TCEC with both scale bits
+    dyn = prepare_dyn_params(h, flag_id, id_a, id_b);
     gemm_mode = CUMPSGEMM_FP16TCEC;
   }
   if (stats_id_a_out) *stats_id_a_out = id_a;
   if (stats_id_b_out) *stats_id_b_out = id_b;
   if (flag_id_out) *flag_id_out = flag_id;
-  const DynParams *dyn = prepare_dyn_params(h, flag_id, id_a, id_b);
   return gemm_dispatch<T>(h, op_A, op_B, m, n, k, alpha, a, lda, stridea, b, ldb, strideb, beta, c,
                           ldc, stridec, batch, gemm_mode, dyn, nullptr);
 }

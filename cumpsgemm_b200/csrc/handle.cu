@@ -70,7 +70,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
         cudaSuccess;
   ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
   ok &= cudaMalloc(&h->dev_status, 2 * sizeof(int)) == cudaSuccess; // status, wave counter
-  const size_t scan_scratch_bytes = static_cast<size_t>(h->num_sms) * 8 * 24 + 16;
+  const size_t scan_scratch_bytes = static_cast<size_t>(h->num_sms) * 8 * 24 * 2 + 16;
   ok &= cudaMalloc(&es.dev_scan_scratch, scan_scratch_bytes) == cudaSuccess;
   if (!ok) {
     cuMpSGEMM_destroy(h);

@@ -78,8 +78,8 @@ struct ExpStatsState {
   std::uint32_t current_buffer_id = 1;
   Profiler profiler;
   bool profiling_enabled = false;
-  // Scratch of the one-launch-per-stage scans: one 24-byte record per CTA (num_sms * 8 of
-  // them) followed by the ticket counter, which every launch leaves at zero.
+  // Scratch of the one-launch-per-stage scans: for each of two operands one 24-byte record per
+  // CTA (num_sms * 8 of them), then two ticket counters, which every launch leaves at zero.
   void *dev_scan_scratch = nullptr;
 };
 
@@ -215,6 +215,12 @@ void exp_stats_decide2(cuMpSGEMM_handle *h, unsigned id);
 template <class T>
 void exp_max_only(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
                   unsigned ld, unsigned batch, unsigned stride);
+// Statistics (full) or maximum exponent only of both operands of a GEMM in shared launches;
+// the slots receive what two separate exp_stats_ext / exp_max_ext calls would leave.
+template <class T>
+void exp_stats_pair(cuMpSGEMM_handle *h, bool full, unsigned id_a, unsigned am, unsigned an,
+                    const T *a, unsigned lda, unsigned stride_a, unsigned id_b, unsigned bm,
+                    unsigned bn, const T *b, unsigned ldb, unsigned stride_b, unsigned batch);
 unsigned next_exp_stats_id(cuMpSGEMM_handle *h);
 unsigned next_dyn_launch_id(cuMpSGEMM_handle *h);
 
@@ -227,6 +233,10 @@ void launch_scaling(cuMpSGEMM_handle *h, ScaleOp op, unsigned m, unsigned n, T *
 // Fill the next DynParams record from a flag slot and two statistics slots.
 DynParams *prepare_dyn_params(cuMpSGEMM_handle *h, unsigned flag_id, unsigned stats_id_a,
                               unsigned stats_id_b);
+// Same, but first derives the flag slot from the two statistics slots' decisions (what
+// set_dynamic_launch_buffer_by_exp_stats does) in the same launch.
+DynParams *prepare_dyn_params_from_stats(cuMpSGEMM_handle *h, unsigned flag_id,
+                                         unsigned stats_id_a, unsigned stats_id_b);
 
 // FP32 GEMMs whose two short dimensions are 2 (tiny_gemm.cu).  long_is_m: C = op(A)(len x 2)
 // op(B)(2 x 2); otherwise C = op(A)(2 x 2) op(B)(2 x len).  len must be a power of two.

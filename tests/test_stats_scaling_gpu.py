@@ -326,3 +326,54 @@ def test_named_timers(handle, oracle):
         assert r is not None and r[1] == 1 and r[0] > 0
     handle.reset_exp_stats_profiling()
     assert handle.get_exp_stats_profiling_result("exp_stats_1") is None
+
+
+def test_gemm_call_statistics_equal_separate_calls(handle, oracle):
+    """A GEMM call in AUTO / FP16TCEC_SCALING takes the statistics of A and B in shared
+    launches and derives flag and scaling constants in one more; the slots it leaves are the
+    ones separate exp_stats_ext / exp_max_ext calls leave (= the oracle's), for every decision
+    outcome of the pair, and so are flag word and result."""
+    import ctypes as C
+    import torch
+    from cumpsgemm_b200 import _lib, api
+
+    lib = _lib.load()
+    blas = torch.cuda.current_blas_handle()
+    m, n, k = 1100, 1060, 1030                      # above the default rule's size threshold
+    alpha, beta = C.c_float(1.0), C.c_float(0.0)
+    well = lambda s, cnt: oracle.gen_uniform(s, cnt) + np.float32(2.0)
+    tiny = lambda s, cnt: ((oracle.gen_uniform(s, cnt) + np.float32(2.0)) * np.float32(2.0 ** -22)).astype(np.float32)
+    wide = lambda s, cnt: oracle.gen_wide_exponent(s, cnt, -30, 10)
+    # a non-owning view of the interception layer's own handle
+    gh = api.Handle.__new__(api.Handle)
+    gh._lib = lib
+    try:
+        for ga, gb in ((well, well), (tiny, well), (well, tiny), (wide, well), (tiny, wide)):
+            a, b = ga(1, m * k), gb(2, k * n)
+            da, db = _dev(a), _dev(b)
+            for mode in (9, 11):                    # AUTO, FP16TCEC_SCALING
+                assert lib.cuMpSGEMM_hijack_set_compute_mode(mode) == 0
+                dc = torch.zeros(m * n, device="cuda")
+                assert lib.cublasSgemm_v2(blas, 0, 0, m, n, k, C.byref(alpha), da.data_ptr(), m,
+                                          db.data_ptr(), k, C.byref(beta), dc.data_ptr(), m) == 0
+                torch.cuda.synchronize()
+                gh._h = C.c_void_p(lib.cuMpSGEMM_hijack_get_internal_global_handle())
+                id_b = gh.get_current_exp_stats_buffer_id()
+                id_a = id_b - 1
+                if mode == 9:
+                    assert _slot(gh, id_a) == oracle.exp_stats(a, m, k, m)
+                    assert _slot(gh, id_b) == oracle.exp_stats(b, k, n, k)
+                    fid = gh.get_current_dynamic_launch_buffer_id()
+                    want_flag = oracle.flag_from_modes(oracle.exp_stats(a, m, k, m)["mode"],
+                                                       oracle.exp_stats(b, k, n, k)["mode"])
+                    got_mode = int(gh.get_dynamic_launch_gemm_compute_mode(fid))
+                    sa, sb = gh.get_dynamic_launch_scaling_mode_AB(fid)
+                    assert (got_mode | (0x40 if sa else 0) | (0x20 if sb else 0)) == want_flag
+                else:
+                    assert gh.get_max_exp(id_a) == oracle.exp_max(a, m, k, m)
+                    assert gh.get_max_exp(id_b) == oracle.exp_max(b, k, n, k)
+                truth = oracle.gemm_f64(0, 0, m, n, k, 1.0, a, m, b, k, 0.0, None, m)
+                assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    finally:
+        lib.cuMpSGEMM_hijack_unset_compute_mode()
+        gh._h = None
