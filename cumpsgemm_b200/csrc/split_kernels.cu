@@ -333,15 +333,11 @@ __device__ __forceinline__ void split_dispatch(const SplitParams &p, int path, c
     else split_generic_body<KIND, 2>(p, bid, tile);
     return;
   }
+  // Both operands of a call are real or both complex, and complex ones never take a
+  // vectorised body, so this instantiation leaves the complex bodies (and their registers) out.
   switch (path) {
   case kPathReal:
     split_generic_body<KIND, 0>(p, bid, tile);
-    break;
-  case kPathComplexA:
-    split_generic_body<KIND, 1>(p, bid, tile);
-    break;
-  case kPathComplexB:
-    split_generic_body<KIND, 2>(p, bid, tile);
     break;
   case kPathKContig:
     split_kcontig_body<KIND>(p, bid);
@@ -361,7 +357,7 @@ struct SplitJob {
 };
 
 template <int KIND, bool VEC>
-__global__ void __launch_bounds__(THREADS) split_dual_kernel(const SplitJob a, const SplitJob b) {
+__global__ void __launch_bounds__(THREADS, VEC ? 5 : 6) split_dual_kernel(const SplitJob a, const SplitJob b) {
   __shared__ float tile[TILE][TILE + 1]; // transposing staging tile shared by all paths
   const uint32_t blocks_a = a.gx * a.gy * a.gz;
   uint32_t id = blockIdx.x;
