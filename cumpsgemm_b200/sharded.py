@@ -17,7 +17,7 @@ two counters); every rank then takes the same decision as a 1-GPU run would.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Tuple
 
 from .api import CUBLAS_OP_N, ComputeMode, Handle
 

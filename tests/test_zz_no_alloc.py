@@ -12,7 +12,6 @@ Frobenius residual below 2^-23 * sqrt(K)) plus equality as the stronger check.
 Collected last on purpose: a run that stops at the first failure has then already run every
 other test.  It does not depend on state left by other tests and passes in a fresh process.
 """
-import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
