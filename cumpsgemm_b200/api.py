@@ -219,6 +219,11 @@ class Handle:
     def set_workspace_limit(self, nbytes: int) -> None:
         self._lib.cuMpSGEMM_set_workspace_limit(self._h, nbytes)
 
+    def set_count_tail_padding(self, enable: bool) -> None:
+        """Count the zeros the reference appends to matrices whose element count is not a
+        multiple of 4 (src/exp_stats.cu:101-116); off by default."""
+        self._lib.cuMpSGEMM_set_count_tail_padding(self._h, 1 if enable else 0)
+
     def set_debug_buffer(self, dev_words8) -> None:
         """Stall-breakdown buffer (8 x int64 CUDA tensor) or None."""
         self._lib.cuMpSGEMM_set_debug_buffer(self._h, 0 if dev_words8 is None else _ptr(dev_words8))

@@ -13,9 +13,12 @@
 //   readback                 :607-629
 // Differences, all deliberate: the matrix is read with 128-bit loads in a
 // persistent grid sized to the SM count; per-CTA partial counts stay integers
-// (the reference stages them through float shared memory); the zero padding
-// the reference adds when m*n is not a multiple of 4 is not counted; index
-// arithmetic is 64-bit throughout.
+// (the reference stages them through float shared memory); index arithmetic is
+// 64-bit throughout; the zero padding the reference's 4-wide loop appends (and
+// counts) when m*n is not a multiple of 4 (:101-116, :222-238) is counted only
+// when the handle asks for it (cuMpSGEMM_set_count_tail_padding or
+// CUMPSGEMM_COUNT_TAIL_PADDING=1), because it is a defect of the counting loop:
+// the default counts exactly the matrix elements.
 #include "internal.hpp"
 
 namespace cumpsgemm_b200 {
@@ -34,12 +37,20 @@ struct ScanParams {
   uint64_t chunks_per_col;
   uint64_t items;     // batch * n * chunks_per_col
   int vec_ok;         // pointer, ld and stride allow aligned float4 access
+  // Zero values the reference's stage kernels append to the tail of every matrix when m*n is
+  // not a multiple of 4 and then count like data (0 unless the compatibility switch is on).
+  unsigned long long pad_values;
 };
 
 // Collapse contiguous storage into one long column so that small matrices still vectorise.
 ScanParams make_scan(const void *ptr, uint64_t m, uint64_t n, uint64_t ld, uint32_t batch,
-                     uint64_t stride, int floats_per_elem) {
+                     uint64_t stride, int floats_per_elem, bool count_tail_padding = false) {
   ScanParams s;
+  s.pad_values = 0;
+  if (count_tail_padding) {
+    const uint64_t matrices = (stride == 0) ? 1u : batch;
+    s.pad_values = ((4 - (m * n) % 4) % 4) * static_cast<uint64_t>(floats_per_elem) * matrices;
+  }
   s.ptr = reinterpret_cast<const float *>(ptr);
   s.m = m * floats_per_elem;
   s.n = n;
@@ -130,14 +141,31 @@ __device__ __forceinline__ void scan_items(const ScanParams &s, Acc &a, float ig
   }
 }
 
+// The padded zeros of the compatibility mode, counted once per operand (by thread 0 of its
+// first CTA) under the stage's thresholds: |0| >= ignore -> total, and 0 < underflow
+// threshold -> underflow.
+struct PadCounts {
+  unsigned long long total, underflow;
+};
+__device__ __forceinline__ PadCounts pad_counts(const ScanParams &s, unsigned int bid,
+                                                float ignore_thr, float uf_thr) {
+  PadCounts p{0ull, 0ull};
+  if (s.pad_values != 0 && bid == 0 && threadIdx.x == 0 && 0.f >= ignore_thr) {
+    p.total = s.pad_values;
+    if (0.f < uf_thr) p.underflow = s.pad_values;
+  }
+  return p;
+}
+
 template <bool COUNT, bool MAXV>
 __device__ __forceinline__ void reduce_and_publish(Acc acc, float *max_slot,
                                                    unsigned long long *total_slot,
-                                                   unsigned long long *uf_slot) {
+                                                   unsigned long long *uf_slot,
+                                                   PadCounts pad = PadCounts{0ull, 0ull}) {
   struct {
     float max_abs;
     unsigned long long total, underflow;
-  } a{acc.max_abs, acc.total, acc.underflow};
+  } a{acc.max_abs, acc.total + pad.total, acc.underflow + pad.underflow};
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) {
     if (MAXV) a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, off));
@@ -187,7 +215,8 @@ __global__ void __launch_bounds__(THREADS)
                   unsigned long long *uf_slot, float ignore_thr, float uf_thr) {
   Acc a{0.f, 0u, 0u};
   scan_items<true, true>(s, a, ignore_thr, uf_thr);
-  reduce_and_publish<true, true>(a, max_slot, total_slot, uf_slot);
+  reduce_and_publish<true, true>(a, max_slot, total_slot, uf_slot,
+                                 pad_counts(s, blockIdx.x, ignore_thr, uf_thr));
 }
 
 __global__ void decide1_kernel(int *mode, const float *max_slot, unsigned long long *total_slot,
@@ -211,7 +240,8 @@ __global__ void __launch_bounds__(THREADS)
   const float mx = *max_slot;
   Acc a{0.f, 0u, 0u};
   scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx);
-  reduce_and_publish<true, false>(a, nullptr, total_slot, uf_slot);
+  reduce_and_publish<true, false>(a, nullptr, total_slot, uf_slot,
+                                  pad_counts(s, blockIdx.x, half_ignore_thr * mx, half_uf_thr * mx));
 }
 
 __global__ void decide2_kernel(int *mode, const unsigned long long *total_slot,
@@ -282,8 +312,10 @@ __device__ __forceinline__ ScanTotals block_reduce(ScanTotals a) {
 // *out; false everywhere else.
 __device__ __forceinline__ bool grid_reduce(Acc acc, ScanPartial *partials, unsigned int *ticket,
                                             ScanTotals *out, unsigned int bid = blockIdx.x,
-                                            unsigned int nblocks = gridDim.x) {
-  const ScanTotals mine = block_reduce(ScanTotals{acc.max_abs, acc.total, acc.underflow});
+                                            unsigned int nblocks = gridDim.x,
+                                            PadCounts pad = PadCounts{0ull, 0ull}) {
+  const ScanTotals mine = block_reduce(
+      ScanTotals{acc.max_abs, acc.total + pad.total, acc.underflow + pad.underflow});
   __shared__ bool s_last;
   if (threadIdx.x == 0) {
     ScanPartial rec;
@@ -324,7 +356,8 @@ __device__ __forceinline__ void fused_stage1_body(const ScanParams &s, const Sta
   Acc a{0.f, 0u, 0u};
   scan_items<true, true>(s, a, ignore_thr, uf_thr, bid, nblocks);
   ScanTotals t;
-  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks)) return;
+  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks, pad_counts(s, bid, ignore_thr, uf_thr)))
+    return;
   // keep only the exponent field: 2^floor(log2 max|x|) as a float
   const float mx = __uint_as_float(__float_as_uint(t.max_abs) & 0x7f800000u);
   *o.max_slot = mx;
@@ -351,7 +384,9 @@ __device__ __forceinline__ void fused_stage2_body(const ScanParams &s, const Sta
   Acc a{0.f, 0u, 0u};
   scan_items<true, false>(s, a, half_ignore_thr * mx, half_uf_thr * mx, bid, nblocks);
   ScanTotals t;
-  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks)) return;
+  if (!grid_reduce(a, partials, ticket, &t, bid, nblocks,
+                   pad_counts(s, bid, half_ignore_thr * mx, half_uf_thr * mx)))
+    return;
   *o.total_slot = t.total;
   *o.uf_slot = t.underflow;
   *o.mode = (static_cast<float>(t.underflow) <= static_cast<float>(t.total) * tolerance)
@@ -506,7 +541,8 @@ void exp_stats_init_slot(cuMpSGEMM_handle *h, unsigned id) {
 template <class T>
 void exp_stats_stage1(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
                       unsigned ld, unsigned batch, unsigned stride) {
-  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
+  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>(),
+                                 h->exp_stats.count_tail_padding);
   stage1_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
       s, h->exp_stats.dev_max + id, h->exp_stats.dev_total + id, h->exp_stats.dev_underflow + id,
       h->exp_stats.ignore_threshold, h->exp_stats.underflow_threshold);
@@ -521,7 +557,8 @@ void exp_stats_decide1(cuMpSGEMM_handle *h, unsigned id) {
 template <class T>
 void exp_stats_stage2(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
                       unsigned ld, unsigned batch, unsigned stride) {
-  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
+  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>(),
+                                 h->exp_stats.count_tail_padding);
   stage2_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
       s, h->exp_stats.dev_mode + id, h->exp_stats.dev_max + id, h->exp_stats.dev_total + id,
       h->exp_stats.dev_underflow + id, h->exp_stats.ignore_threshold / 2,
@@ -564,7 +601,8 @@ inline StatSlots stat_slots(cuMpSGEMM_handle *h, unsigned id) {
 template <class T>
 void exp_stats_fused(cuMpSGEMM_handle *h, unsigned id, unsigned m, unsigned n, const T *ptr,
                      unsigned ld, unsigned batch, unsigned stride) {
-  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>());
+  const ScanParams s = make_scan(ptr, m, n, ld, batch, stride, floats_per_elem<T>(),
+                                 h->exp_stats.count_tail_padding);
   auto &es = h->exp_stats;
   fused_stage1_kernel<<<scan_grid(h, s), THREADS, 0, h->cuda_stream>>>(
       s, stat_slots(h, id), es.ignore_threshold, es.underflow_threshold,
@@ -589,8 +627,9 @@ void exp_stats_pair(cuMpSGEMM_handle *h, bool full, unsigned id_a, unsigned am, 
                     const T *a, unsigned lda, unsigned stride_a, unsigned id_b, unsigned bm,
                     unsigned bn, const T *b, unsigned ldb, unsigned stride_b, unsigned batch) {
   DualScan d;
-  d.s[0] = make_scan(a, am, an, lda, batch, stride_a, floats_per_elem<T>());
-  d.s[1] = make_scan(b, bm, bn, ldb, batch, stride_b, floats_per_elem<T>());
+  const bool pad = full && h->exp_stats.count_tail_padding;
+  d.s[0] = make_scan(a, am, an, lda, batch, stride_a, floats_per_elem<T>(), pad);
+  d.s[1] = make_scan(b, bm, bn, ldb, batch, stride_b, floats_per_elem<T>(), pad);
   d.o[0] = stat_slots(h, id_a);
   d.o[1] = stat_slots(h, id_b);
   d.grid_a = scan_grid(h, d.s[0]);

@@ -219,6 +219,10 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t h, size_t bytes) {
   h->workspace_limit_bytes = bytes;
 }
 
+void cuMpSGEMM_set_count_tail_padding(cuMpSGEMM_handle_t h, int enable) {
+  h->exp_stats.count_tail_padding = (enable != 0);
+}
+
 void cuMpSGEMM_set_debug_buffer(cuMpSGEMM_handle_t h, unsigned long long *dev_words8) {
   h->debug_buffer = dev_words8;
 }

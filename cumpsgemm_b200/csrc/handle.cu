@@ -91,6 +91,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
     cuMpSGEMM_destroy(h);
     return CUBLAS_STATUS_EXECUTION_FAILED;
   }
+  h->exp_stats.count_tail_padding = env_flag("CUMPSGEMM_COUNT_TAIL_PADDING", false);
   const char *ws_env = std::getenv("CUMPSGEMM_WORKSPACE_LIMIT_MB");
   if (ws_env != nullptr) h->workspace_limit_bytes = std::strtoull(ws_env, nullptr, 10) << 20;
   *handle = h;

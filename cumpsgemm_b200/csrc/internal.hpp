@@ -78,6 +78,9 @@ struct ExpStatsState {
   std::uint32_t current_buffer_id = 1;
   Profiler profiler;
   bool profiling_enabled = false;
+  // Compatibility switch: also count the zeros the reference's 4-wide counting loop appends
+  // to a matrix whose element count is not a multiple of 4 (src/exp_stats.cu:101-116).
+  bool count_tail_padding = false;
   // Scratch of the one-launch-per-stage scans: for each of two operands one 24-byte record per
   // CTA (num_sms * 8 of them), then two ticket counters, which every launch leaves at zero.
   void *dev_scan_scratch = nullptr;

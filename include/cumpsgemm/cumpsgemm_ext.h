@@ -134,6 +134,15 @@ int cuMpSGEMM_selftest_bounded_wait(cuMpSGEMM_handle_t handle, unsigned limit_ms
 /* Cap (bytes) for the operand workspace a strided-batch call may use at once; batches beyond
  * it are processed in chunks.  0 restores the default (8 GiB). */
 void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
+/* Compatibility switch for the exponent statistics (off by default; also set by the
+ * environment variable CUMPSGEMM_COUNT_TAIL_PADDING=1 at handle creation).  The reference's
+ * counting kernels walk a matrix four elements at a time and, when m*n is not a multiple of
+ * 4, append zeros to the last group and count them like data
+ * (reference: src/exp_stats.cu:101-116 and :222-238).  With the switch on, exp_stats_ext
+ * adds the same (4 - m*n % 4) % 4 zero elements per matrix to `total` (and to `underflow`
+ * when 0 is below the stage's threshold), so counts and decisions equal the reference's for
+ * such shapes too; with it off only real matrix elements are counted. */
+void cuMpSGEMM_set_count_tail_padding(cuMpSGEMM_handle_t handle, int enable);
 /* Per-launch device timing with CUDA events on the handle's stream (off by default).  While
  * enabled every split + GEMM launch group records three events; get_kernel_timing
  * synchronises the stream, returns the number of launch groups since the last query and the

@@ -28,6 +28,7 @@
  *   oracle_scale : src/dynamic_scaling.cu:75-150 (scale_A/B, scale_C, reset).
  */
 #include <math.h>
+#include <omp.h>
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -40,6 +41,14 @@ enum {
   MODE_UNDEFINED = 10,
   MODE_FP16TCEC_SCALING = 11
 };
+
+/* ------------------------------------------------------------------ host threads
+ * Launchers that start several processes per machine export OMP_NUM_THREADS=1; the timed
+ * CPU baseline asks for the cores it is allowed to use explicitly. */
+void oracle_set_num_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+int oracle_get_max_threads(void) { return omp_get_max_threads(); }
 
 /* ------------------------------------------------------------------ FP64 truth */
 static inline float lda_at(const float *a, int op, size_t r, size_t kk, size_t ld) {

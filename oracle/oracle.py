@@ -34,12 +34,21 @@ class _Stats(C.Structure):
                 ("mode", C.c_int)]
 
 
+def reference_tree():
+    """Root of a checkout of the reference project, or None.  Taken from the environment
+    variable CUMPSGEMM_REFERENCE_TREE; without it, a sibling directory `reference` of this
+    repository is used when it exists."""
+    env = os.environ.get("CUMPSGEMM_REFERENCE_TREE")
+    cand = Path(env) if env else HERE.parent.parent / "reference"
+    return cand if (cand / "src" / "exp_stats.cu").exists() else None
+
+
 def build(with_ref: bool = False) -> None:
     """Compile liboracle.so (and, when asked and possible, the reference-derived objects)."""
     subprocess.run(["make", "-C", str(HERE)], check=True, capture_output=True)
-    ref = Path(os.environ.get("CUMPSGEMM_REFERENCE_TREE", "/root/reference"))
-    if with_ref and (ref / "src").exists():
-        subprocess.run(["make", "-C", str(HERE), "ref", f"REF={ref}"], check=True,
+    ref = reference_tree()
+    if with_ref and ref is not None:
+        subprocess.run(["make", "-C", str(HERE), "ref", "ref_gpu", f"REF={ref}"], check=True,
                        capture_output=True)
 
 
@@ -53,6 +62,14 @@ def lib():
         _lib.oracle_exp_max.restype = C.c_float
         _lib.oracle_flag_from_modes.restype = C.c_int
     return _lib
+
+
+def set_num_threads(n: int) -> int:
+    """Use `n` OpenMP threads in the oracle's loops (whatever OMP_NUM_THREADS says) and return
+    the number the runtime then reports."""
+    L = lib()
+    L.oracle_set_num_threads(int(n))
+    return int(L.oracle_get_max_threads())
 
 
 def _fp(a: np.ndarray):
@@ -246,3 +263,87 @@ def gen_unit_frobenius_complex(seed, batch, rows, cols):
     z = (re + 1j * im).astype(np.complex64)
     nrm = np.sqrt((np.abs(z.astype(np.complex128)) ** 2).sum(axis=1, keepdims=True))
     return (z / nrm).astype(np.complex64).ravel()
+
+
+# ------------------------------------------------------------------------ the reference itself
+class ReferenceStats:
+    """The reference's own statistics / scaling / flag code running on the GPU.
+
+    ``_ref/libref_stats.so`` is the reference's src/exp_stats.cu, src/dynamic_scaling.cu and
+    src/dynamic_launch.cu compiled unmodified for sm_100a (``make ref_gpu``; only where the
+    reference tree is available, the built library then travels with the repository).  Device
+    buffers are passed as raw addresses; every getter synchronises.  Checker only.
+    """
+
+    PATH = REF_DIR / "libref_stats.so"
+
+    @classmethod
+    def available(cls) -> bool:
+        return cls.PATH.exists()
+
+    def __init__(self):
+        L = C.CDLL(str(self.PATH))
+        vp, u32 = C.c_void_p, C.c_uint
+        L.ref_create.restype = vp
+        L.ref_destroy.argtypes = [vp]
+        L.ref_set_exp_stats_params.argtypes = [vp, C.c_float, C.c_float, C.c_float]
+        for name in ("ref_exp_stats_ext_s", "ref_exp_stats_ext_c", "ref_exp_max_ext_s",
+                     "ref_exp_max_ext_c"):
+            fn = getattr(L, name)
+            fn.restype = u32
+            fn.argtypes = [vp, u32, u32, vp, u32, u32, u32]
+        L.ref_get_exp_stats.argtypes = [vp, u32, C.POINTER(C.c_ulonglong),
+                                        C.POINTER(C.c_ulonglong)]
+        L.ref_get_max_exp.restype = C.c_float
+        L.ref_get_max_exp.argtypes = [vp, u32]
+        L.ref_get_compute_mode_level.restype = C.c_int
+        L.ref_get_compute_mode_level.argtypes = [vp, u32]
+        L.ref_next_flag_id.restype = u32
+        L.ref_next_flag_id.argtypes = [vp]
+        L.ref_set_flag_by_exp_stats.argtypes = [vp, u32, u32, u32]
+        L.ref_get_flag.restype = C.c_int
+        L.ref_get_flag.argtypes = [vp, u32]
+        for name in ("ref_scale_s", "ref_scale_c"):
+            getattr(L, name).argtypes = [vp, C.c_int, u32, u32, vp, u32, u32, u32, u32, u32, u32]
+        self._L = L
+        self._h = vp(L.ref_create())
+
+    def close(self):
+        if self._h:
+            self._L.ref_destroy(self._h)
+            self._h = None
+
+    def set_exp_stats_params(self, ignore_threshold, underflow_threshold, tolerance):
+        self._L.ref_set_exp_stats_params(self._h, ignore_threshold, underflow_threshold, tolerance)
+
+    def exp_stats_ext(self, m, n, dev_ptr: int, ld, batch=1, stride=0, complex=False) -> int:
+        fn = self._L.ref_exp_stats_ext_c if complex else self._L.ref_exp_stats_ext_s
+        return fn(self._h, m, n, dev_ptr, ld, batch, stride)
+
+    def exp_max_ext(self, m, n, dev_ptr: int, ld, batch=1, stride=0, complex=False) -> int:
+        fn = self._L.ref_exp_max_ext_c if complex else self._L.ref_exp_max_ext_s
+        return fn(self._h, m, n, dev_ptr, ld, batch, stride)
+
+    def slot(self, sid: int) -> dict:
+        uf, total = C.c_ulonglong(0), C.c_ulonglong(0)
+        self._L.ref_get_exp_stats(self._h, sid, C.byref(uf), C.byref(total))
+        return {"max_exp": float(self._L.ref_get_max_exp(self._h, sid)), "total": total.value,
+                "underflow": uf.value, "mode": int(self._L.ref_get_compute_mode_level(self._h, sid))}
+
+    def max_exp(self, sid: int) -> float:
+        return float(self._L.ref_get_max_exp(self._h, sid))
+
+    def flag_from_stats(self, sid_a: int, sid_b: int):
+        """(flag id, flag word) after set_dynamic_launch_buffer_by_exp_stats on a fresh slot."""
+        fid = self._L.ref_next_flag_id(self._h)
+        self._L.ref_set_flag_by_exp_stats(self._h, fid, sid_a, sid_b)
+        return fid, int(self._L.ref_get_flag(self._h, fid))
+
+    def flag(self, fid: int) -> int:
+        return int(self._L.ref_get_flag(self._h, fid))
+
+    def scale(self, what: int, m, n, dev_ptr: int, ld, batch, stride, sid_a, sid_b, flag_id,
+              complex=False):
+        """what: SCALE_A, SCALE_B, SCALE_C, RESET_A, RESET_B (in place, on the device)."""
+        fn = self._L.ref_scale_c if complex else self._L.ref_scale_s
+        fn(self._h, what, m, n, dev_ptr, ld, batch, stride, sid_a, sid_b, flag_id)

@@ -205,3 +205,31 @@ def test_tiny_gemm_restatement_against_fp64(oracle, cplx, long_is_m, op_a, op_b)
     g2 = got.reshape(batch, c_rc[1], ldc)
     c2 = c0.reshape(batch, c_rc[1], ldc)
     assert np.array_equal(g2[:, :, c_rc[0]:], c2[:, :, c_rc[0]:])
+
+
+def test_reference_checker_library_exports_its_entry_points(oracle):
+    """oracle/_ref/libref_stats.so (the reference's own statistics / scaling sources compiled for
+    sm_100a) loads without a GPU and exports every entry point the GPU pin test calls."""
+    import ctypes as C
+
+    if not oracle.ReferenceStats.available():
+        pytest.skip("reference checker not built (the reference tree was absent at build time)")
+    L = C.CDLL(str(oracle.ReferenceStats.PATH))
+    for name in ("ref_create", "ref_destroy", "ref_set_exp_stats_params", "ref_exp_stats_ext_s",
+                 "ref_exp_stats_ext_c", "ref_exp_max_ext_s", "ref_exp_max_ext_c",
+                 "ref_get_exp_stats", "ref_get_max_exp", "ref_get_compute_mode_level",
+                 "ref_next_flag_id", "ref_set_flag_by_exp_stats", "ref_get_flag", "ref_scale_s",
+                 "ref_scale_c"):
+        assert hasattr(L, name), name
+
+
+def test_oracle_thread_control(oracle):
+    """The timed CPU baseline asks for its threads explicitly (launchers that start one process
+    per GPU export OMP_NUM_THREADS=1)."""
+    import os
+
+    try:
+        assert oracle.set_num_threads(2) == 2
+        assert oracle.set_num_threads(1) == 1
+    finally:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
