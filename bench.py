@@ -19,8 +19,24 @@ The JSON line also carries
   roofline     : the GEMM kernel's own device time (CUDA events on the launching
                  stream around the kernel, recorded by the library) against the
                  emulation roofline = measured dense 16-bit tensor peak / 3 MMAs;
+  rel_err      : the accuracy half of the metric, checked after the timed region
+                 on every rank: one more call on a fresh copy of C, compared on
+                 sampled rows and columns with an FP64 product computed on the GPU
+                 (relative Frobenius residual, the reference's criterion
+                 residual < 2^-23*sqrt(K), test/main.cu:68-74; max and mean
+                 relative error), next to cuBLAS FP32 SGEMM on the same inputs.
+                 The worst rank is reported; the run exits non-zero above the
+                 threshold;
+  aux_roofline : HBM-bound helpers (split pass, exponent statistics, maximum
+                 exponent, scaling) in GB/s against the measured copy bandwidth
+                 (N = 1 only);
+  batch_sharded: strided-batch throughput with the batch spread over the ranks
+                 (complex 512 x 256^3 in FP16TCEC_SCALING, strong scaling; real
+                 8 x 8192^3 per rank in AUTO, weak scaling), statistics
+                 all-reduces included, one sampled batch checked against FP64;
   e2e          : the same metric with A, B, C in pinned host memory, host<->device
-                 copies inside the timed region;
+                 copies inside the timed region (N > 1: rank 0 uploads A once and
+                 it reaches the other ranks over NVLink);
   cpu_baseline : FP32 host GEMM (the oracle's register-blocked kernel, all host
                  cores) on a bounded column slice of the same problem (rank 0,
                  N = 1 only).
@@ -143,12 +159,22 @@ def make_inputs_device(torch, n_rows, n_cols_b, k, seed, device):
     return a, b, c
 
 
-def cpu_gemm_sample(n_full: int, target_seconds: float, seed: int = 1):
-    """Times the oracle's FP32 host GEMM on a column slice of the n_full^3 problem.
-    Returns (TFLOP/s, seconds, columns)."""
-    import numpy as np
+def oracle_with_all_cores():
+    """The CPU oracle with as many OpenMP threads as this process may use.  torchrun exports
+    OMP_NUM_THREADS=1 when it starts several ranks; the timed CPU arm must not inherit that."""
+    cores = host_cores()
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     from oracle import oracle as orc
 
+    return orc, orc.set_num_threads(cores)
+
+
+def cpu_gemm_sample(n_full: int, target_seconds: float, seed: int = 1):
+    """Times the oracle's FP32 host GEMM on a column slice of the n_full^3 problem.
+    Returns (TFLOP/s, seconds, columns, threads)."""
+    import numpy as np
+
+    orc, threads = oracle_with_all_cores()
     m = k = n_full
     rng = orc.rng(seed)
     a = rng.uniform(-1, 1, size=m * k).astype(np.float32)
@@ -166,7 +192,7 @@ def cpu_gemm_sample(n_full: int, target_seconds: float, seed: int = 1):
     t0 = time.perf_counter()
     orc.gemm_f32(0, 0, m, cols, k, 1.0, a, m, b, k, 0.0, c, m)
     dt = time.perf_counter() - t0
-    return 2.0 * m * cols * k / dt / 1e12, dt, cols
+    return 2.0 * m * cols * k / dt / 1e12, dt, cols, threads
 
 
 def run_reference(args, rank, world):
@@ -174,15 +200,14 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     import numpy as np
-    from oracle import oracle as orc
 
+    orc, threads = oracle_with_all_cores()
     n_full = args.n
     m = k = n_full
-    cores = host_cores()
     rng = orc.rng(1)
     a = rng.uniform(-1, 1, size=m * k).astype(np.float32)
     # size one step at about 3 s
-    tf, dt, cols = cpu_gemm_sample(n_full, 3.0)
+    tf, dt, cols, _ = cpu_gemm_sample(n_full, 3.0)
     b = rng.uniform(-1, 1, size=k * cols).astype(np.float32)
     c = rng.uniform(-1, 1, size=m * cols).astype(np.float32)
     for _ in range(args.warmup):
@@ -194,7 +219,8 @@ def run_reference(args, rank, world):
     ms = dt / args.steps * 1e3
     value = 2.0 * m * cols * k * args.steps / dt / 1e12
     sample = (f"FP32 host GEMM (oracle port of the path's arithmetic in plain FP32), m=k={n_full}, "
-              f"{cols} of {n_full} columns per step, all {cores} host threads")
+              f"{cols} of {n_full} columns per step, {threads} OpenMP threads "
+              f"(omp_get_max_threads; {host_cores()} cores in the affinity mask)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -202,12 +228,234 @@ def run_reference(args, rank, world):
         "config": {"workload": f"FP32 SGEMM m=k={n_full}, column slice n={cols}, alpha=1, beta=0.5",
                    "note": "the reference's GPU kernels (sm_80/sm_86, absent submodules) cannot "
                            "be built; this arm is the CPU restatement on host cores"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------- accuracy
+SAMPLE_ROWS = 6
+SAMPLE_COLS = 4
+
+
+def sample_indices(m, n):
+    rows = sorted({0, 1, min(127, m - 1), min(128, m - 1), min(m // 2 + 3, m - 1), m - 1})
+    cols = sorted({0, min(255, n - 1), min(256, n - 1), n - 1})
+    return rows, cols
+
+
+def fp64_samples(torch, a, b, c0, m, n, k, beta, rows, cols, chunk=2048):
+    """FP64 truth of alpha=1, op N/N on the sampled rows (returned as n x len(rows)) and
+    columns (len(cols) x m) of column-major flat operands, computed on the GPU in chunks so
+    that no full-size FP64 copy of an operand is made."""
+    av, bv, cv = a.view(k, m), b.view(n, k), c0.view(n, m)      # av[l, i] = A(i, l) etc.
+    a_rows = av[:, rows].double()                               # k x R
+    t_rows = torch.empty(n, len(rows), dtype=torch.float64, device=a.device)
+    for j0 in range(0, n, chunk):
+        j1 = min(n, j0 + chunk)
+        t_rows[j0:j1] = bv[j0:j1].double() @ a_rows
+    t_rows += beta * cv[:, rows].double()
+    b_cols = bv[cols].double()                                  # Ccount x k
+    t_cols = torch.zeros(len(cols), m, dtype=torch.float64, device=a.device)
+    for l0 in range(0, k, chunk):
+        l1 = min(k, l0 + chunk)
+        t_cols += b_cols[:, l0:l1] @ av[l0:l1].double()
+    t_cols += beta * cv[cols].double()
+    return t_rows, t_cols
+
+
+def sampled_errors(torch, truth_rows, truth_cols, got_flat, m, n, rows, cols):
+    gv = got_flat.view(n, m)
+    t = torch.cat([truth_rows.reshape(-1), truth_cols.reshape(-1)])
+    g = torch.cat([gv[:, rows].double().reshape(-1), gv[cols].double().reshape(-1)])
+    diff = (t - g).abs()
+    residual = (diff.pow(2).sum() / t.pow(2).sum()).sqrt().item()
+    nz = t != 0
+    rel = diff[nz] / t[nz].abs()
+    return residual, rel.max().item(), rel.mean().item()
+
+
+def accuracy_block(torch, dist, device, step_into, a, b, c0, m, n, k, beta):
+    """One more call on a fresh copy of C, compared with FP64 on sampled rows and columns; the
+    same for cuBLAS FP32 SGEMM.  Worst rank wins."""
+    rows, cols = sample_indices(m, n)
+    c_chk = c0.clone()
+    step_into(c_chk)
+    torch.cuda.synchronize()
+    t_rows, t_cols = fp64_samples(torch, a, b, c0, m, n, k, beta, rows, cols)
+    res, mx, mean = sampled_errors(torch, t_rows, t_cols, c_chk, m, n, rows, cols)
+    del c_chk
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    # column-major C = A B  <=>  row-major C^T (n x m) = B^T (n x k) A^T (k x m)
+    c32 = torch.addmm(c0.view(n, m), b.view(n, k), a.view(k, m), beta=beta, alpha=1.0)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    res32, mx32, mean32 = sampled_errors(torch, t_rows, t_cols, c32.reshape(-1), m, n, rows, cols)
+    del c32
+    vals = torch.tensor([res, mx, mean, res32, mx32, mean32], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    res, mx, mean, res32, mx32, mean32 = (float(v) for v in vals.tolist())
+    threshold = 2.0 ** -23 * (k ** 0.5)
+    return {
+        "residual": res, "threshold": threshold, "max": mx, "mean": mean,
+        "fp32_simt_residual": res32, "fp32_simt_max": mx32, "fp32_simt_mean": mean32,
+        "passed": bool(res < threshold),
+        "samples": f"rows {rows} and columns {cols} of every rank's C block "
+                   f"({len(rows) * n + len(cols) * m} entries per rank), FP64 truth computed on "
+                   "the GPU; worst rank reported",
+        "comparator": "cuBLAS FP32 SGEMM (torch.addmm, TF32 off) on the same inputs",
+    }, (rows, t_rows)
+
+
+def host_row_check(torch, a, b, c0, m, n, k, beta, row, truth_row_gpu):
+    """Cross-check of the GPU's FP64 truth on one row against the host oracle's FP64 GEMM."""
+    import numpy as np
+
+    orc, _ = oracle_with_all_cores()
+    ah, bh, ch = a.cpu().numpy(), b.cpu().numpy(), c0.cpu().numpy()
+    truth = orc.gemm_f64(0, 0, 1, n, k, 1.0, ah[row:], m, bh, k, beta, ch[row:], m).reshape(-1)
+    g = truth_row_gpu.cpu().numpy()
+    return float(np.abs(truth - g).max() / np.abs(truth).max())
+
+
+# ---------------------------------------------------------------------- helpers' bandwidth
+def aux_rooflines(torch, handle, device, split_ms, n_main, hbm):
+    """GB/s of the HBM-bound helpers: the split pass of the main problem (from the library's
+    own events) and statistics / maximum exponent / scaling on 8192 x 8192 FP32 inputs."""
+    out = {}
+
+    def entry(ms, nbytes, what):
+        gbs = nbytes / ms / 1e6
+        return {"ms": ms, "bytes": nbytes, "gbs": gbs, "frac": (gbs / hbm) if hbm else None,
+                "algorithmic_bytes": what}
+
+    if split_ms > 0:
+        out["split_dual_kernel"] = entry(
+            split_ms, 16.0 * n_main * n_main,
+            "2 operands x N^2 x (4 B read + 2 x 2 B hi/lo written)")
+    n = 8192
+    g = torch.Generator(device=device)
+    g.manual_seed(5)
+    sgn = torch.where(torch.rand(n * n, device=device, generator=g) < 0.5, -1.0, 1.0)
+    x = torch.ldexp(sgn * (1 + torch.rand(n * n, device=device, generator=g)),
+                    torch.randint(-30, 11, (n * n,), device=device, generator=g,
+                                  dtype=torch.int32))
+    y = torch.rand(n * n, device=device, generator=g) + 1
+    nbytes = 4.0 * n * n
+    sid = handle.exp_max_ext(n, n, y, n)
+
+    def timeit(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    out["exp_stats_ext (both stages run: wide exponent range)"] = entry(
+        timeit(lambda: handle.exp_stats_ext(n, n, x, n)), 2 * nbytes, "2 passes x m*n*4 B read")
+    out["exp_max_ext"] = entry(timeit(lambda: handle.exp_max_ext(n, n, x, n)), nbytes,
+                               "m*n*4 B read")
+    out["scale_A + reset_scale_A (in place)"] = entry(
+        timeit(lambda: (handle.scale_A(sid, 1, n, n, y, n), handle.reset_scale_A(sid, 1, n, n, y, n))),
+        4 * nbytes, "2 calls x m*n*4 B read + written")
+    return {"unit": "GB/s", "peak": hbm, "peak_source": "measured copy bandwidth",
+            "inputs": f"{n} x {n} FP32 (268 MB, larger than L2), 20 calls each", "kernels": out}
+
+
+# ---------------------------------------------------------------------- batch partition
+def batch_sharded_block(torch, dist, device, sharded, rank, world):
+    """Strided-batch throughput with the batch spread over the ranks, through
+    ShardedGemm.gemm_strided_batch_local (its statistics all-reduces are inside the time)."""
+    from cumpsgemm_b200 import api
+    from cumpsgemm_b200.sharded import batch_range
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, warmup, steps):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def worst(x):
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    g = torch.Generator(device=device)
+    g.manual_seed(4242 + rank)
+    # complex 512 x 256^3, unit Frobenius norm per matrix, FP16TCEC_SCALING; strong scaling
+    total, s = 512, 256
+    b0, b1 = batch_range(total, world, rank)
+    nb = b1 - b0
+
+    def unit(count):
+        z = torch.complex(torch.randn(count, s * s, device=device, generator=g),
+                          torch.randn(count, s * s, device=device, generator=g))
+        return (z / z.abs().pow(2).sum(1, keepdim=True).sqrt()).to(torch.complex64).contiguous()
+
+    za, zb = unit(nb), unit(nb)
+    zc = torch.zeros(nb * s * s, dtype=torch.complex64, device=device)
+    mode = api.ComputeMode.FP16TCEC_SCALING
+    ms = timed(lambda: sharded.gemm_strided_batch_local(0, 0, s, s, s, 1.0, za, s, s * s, zb, s,
+                                                        s * s, 0.0, zc, s, s * s, nb, mode), 3, 20)
+    i = nb // 2
+    A = za[i].view(s, s).t().to(torch.complex128)
+    B = zb[i].view(s, s).t().to(torch.complex128)
+    got = zc.view(nb, s, s)[i].t().to(torch.complex128)
+    truth = A @ B
+    res = ((truth - got).abs().pow(2).sum() / truth.abs().pow(2).sum()).sqrt().item()
+    out["cgemm_512x256^3_FP16TCEC_SCALING"] = {
+        "scaling": "strong", "batches_per_rank": nb, "ms": ms,
+        "tflops": 8.0 * total * s ** 3 / ms / 1e9,
+        "sampled_batch_residual": worst(res), "threshold": 2.0 ** -23 * s ** 0.5,
+        "collectives": "2 all-reduces per operand (max exponent) when world > 1"}
+    del za, zb, zc
+    # real 8 x 8192^3 per rank, N(0,1), AUTO; weak scaling
+    n, nb = 8192, 8
+    a = torch.randn(nb * n * n, device=device, generator=g)
+    b = torch.randn(nb * n * n, device=device, generator=g)
+    c = torch.zeros(nb * n * n, device=device)
+    mode = api.ComputeMode.AUTO
+    ms = timed(lambda: sharded.gemm_strided_batch_local(0, 0, n, n, n, 1.0, a, n, n * n, b, n,
+                                                        n * n, 0.0, c, n, n * n, nb, mode), 1, 3)
+    i = 5
+    rows = [0, 129, n - 1]
+    Ar = a[i * n * n:(i + 1) * n * n].view(n, n)[:, rows].double()            # k x R
+    truth = b[i * n * n:(i + 1) * n * n].view(n, n).double() @ Ar              # n x R
+    got = c[i * n * n:(i + 1) * n * n].view(n, n)[:, rows].double()
+    res = ((truth - got).pow(2).sum() / truth.pow(2).sum()).sqrt().item()
+    out["sgemm_8x8192^3_per_rank_AUTO"] = {
+        "scaling": "weak", "batches_per_rank": nb, "ms": ms,
+        "tflops": 2.0 * nb * world * n ** 3 / ms / 1e9,
+        "sampled_batch_residual": worst(res), "threshold": 2.0 ** -23 * n ** 0.5,
+        "collectives": "3 all-reduces per operand (max exponent, counters of both stages) "
+                       "when world > 1"}
+    del a, b, c
+    return out
 
 
 def run_ours(args, rank, local_rank, world):
@@ -236,15 +484,19 @@ def run_ours(args, rank, local_rank, world):
     sharded = ShardedGemm(handle)
 
     a, b, c = make_inputs_device(torch, m, n_local, k, seed=1234 + rank, device=device)
+    c0 = c.clone()
     if world > 1 and rank != 0:
         a.zero_()                    # content arrives through the broadcast in every step
 
-    def step():
+    def step_into(c_out):
         if world > 1:
-            sharded.gemm_column_block(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c, m, mode,
-                                      root=0, broadcast_A=True)
+            sharded.gemm_column_block(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c_out, m,
+                                      mode, root=0, broadcast_A=True)
         else:
-            handle.gemm(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c, m, mode)
+            handle.gemm(0, 0, m, n_local, k, 1.0, a, m, b, k, args.beta, c_out, m, mode)
+
+    def step():
+        step_into(c)
 
     def barrier():
         if dist is not None:
@@ -290,56 +542,116 @@ def run_ours(args, rank, local_rank, world):
     tf32 = mode in (api.ComputeMode.TF32TCEC, api.ComputeMode.TF32TC)
     peak = peak_dense / (2.0 if tf32 else 1.0) / mma_per_product
     gemm_ms_avg = gemm_ms / max(groups, 1)
+    split_ms_avg = split_ms / max(groups, 1)
     achieved = 2.0 * m * n_local * k / (gemm_ms_avg * 1e-3) / 1e12 if gemm_ms_avg > 0 else 0.0
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak if peak else None,
         "traffic": MEASURED_DRAM_BYTES.get((mode.name, m, n_local, k)),
         "kernel": "tcec_gemm_pair_kernel (tcgen05 cta_group::2, 256x256 tile per CTA pair)",
-        "kernel_ms": gemm_ms_avg, "split_pass_ms": split_ms / max(groups, 1),
+        "kernel_ms": gemm_ms_avg, "split_pass_ms": split_ms_avg,
         "peak_source": f"{peaks['source']} dense 16-bit tensor peak "
                        f"({'sustained' if long_run else 'burst'}) {peak_dense} TFLOP/s / "
                        f"{'2 (TF32) / ' if tf32 else ''}{mma_per_product} MMAs per product",
     }
 
+    # ---- accuracy (outside the timed region): the other half of the metric
+    rel_err, row_truth = None, None
+    if not args.skip_check:
+        rel_err, row_truth = accuracy_block(torch, dist, device, step_into, a, b, c0, m, n_local,
+                                            k, args.beta)
+
     # ---- end to end through host buffers (rank-local problem, max over ranks)
     e2e = None
     if args.e2e_steps > 0:
         host = api.HostGemm(handle, device)
-        ah = torch.empty(a.numel(), dtype=torch.float32, pin_memory=True)
         bh = torch.empty(b.numel(), dtype=torch.float32, pin_memory=True)
         ch = torch.empty(c.numel(), dtype=torch.float32, pin_memory=True)
-        ah.copy_(a)
         bh.copy_(b)
         ch.copy_(c)
-        # the host path reuses the device-resident tensors as staging buffers
-        host._bufs = {"A": a, "B": b, "C": c}
+        ah = None
+        if rank == 0:
+            ah = torch.empty(a.numel(), dtype=torch.float32, pin_memory=True)
+            ah.copy_(a)
+        # the device tensors of the resident run double as staging buffers
+        host.adopt_staging(A=a, B=b, C=c)
+        side = torch.cuda.Stream(device=device)
         torch.cuda.synchronize()
-        h2d, d2h = host.gemm(0, 0, m, n_local, k, 1.0, ah, m, bh, k, args.beta, ch, m, mode)
+
+        def e2e_step():
+            if world == 1:
+                return host.gemm(0, 0, m, n_local, k, 1.0, ah, m, bh, k, args.beta, ch, m, mode)
+            # rank 0 uploads A once; it reaches the other ranks over NVLink while they already
+            # upload their own B and C blocks
+            caller = torch.cuda.current_stream(device)
+            ev = torch.cuda.Event()
+            ev.record(caller)
+            with torch.cuda.stream(side):
+                side.wait_event(ev)
+                if rank == 0:
+                    a.copy_(ah, non_blocking=True)
+                dist.broadcast(a, src=0)
+                ready = torch.cuda.Event()
+                ready.record(side)
+            h2d, d2h = host.gemm(0, 0, m, n_local, k, 1.0, None, m, bh, k, args.beta, ch, m, mode,
+                                 A_device=a, A_ready=ready)
+            return h2d + (a.numel() * 4 if rank == 0 else 0), d2h
+
+        h2d, d2h = e2e_step()
         barrier()
         e0.record()
         for _ in range(args.e2e_steps):
-            h2d, d2h = host.gemm(0, 0, m, n_local, k, 1.0, ah, m, bh, k, args.beta, ch, m, mode)
+            h2d, d2h = e2e_step()
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+        totals = torch.tensor([e2e_ms, float(h2d), float(d2h)], device=device, dtype=torch.float64)
         if dist is not None:
-            t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
+            dist.all_reduce(totals[0:1], op=dist.ReduceOp.MAX)
+            dist.all_reduce(totals[1:3], op=dist.ReduceOp.SUM)
+        e2e_ms, h2d, d2h = float(totals[0]), int(totals[1]), int(totals[2])
         e2e = {"value": 2.0 * m * (n_local * world) * k / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                "steps": args.e2e_steps,
-               "note": "per rank: api.HostGemm, A, B, C copied from pinned host memory and C "
-                       "copied back inside the timed region, pipelined over 16 column blocks; "
-                       "no NCCL broadcast on this leg"}
+               "note": "api.HostGemm: operands in pinned host memory, copies inside the timed "
+                       "region, pipelined over 16 column blocks per rank; bytes are whole-job "
+                       "sums over the ranks" +
+                       ("" if world == 1 else "; A is uploaded by rank 0 only and broadcast "
+                                              "with NCCL while the other ranks upload B and C")}
+        del bh, ch, ah
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tf, dt, cols = cpu_gemm_sample(n, 15.0)
-        cpu = {"value": tf, "unit": UNIT, "cores": host_cores(), "kind": "port",
+        tf, dt, cols, threads = cpu_gemm_sample(n, 15.0)
+        cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
                "sample": f"FP32 host GEMM on {cols} of {n} columns of an m=k={n} problem "
-                         f"({dt:.1f} s)"}
+                         f"({dt:.1f} s, {threads} OpenMP threads)"}
+        if row_truth is not None:
+            rows, t_rows = row_truth
+            j = rows.index(min(128, m - 1)) if min(128, m - 1) in rows else 0
+            cpu["fp64_truth_cross_check"] = {
+                "row": rows[j],
+                "max_abs_diff_over_max_abs": host_row_check(torch, a, b, c0, m, n_local, k,
+                                                            args.beta, rows[j], t_rows[:, j]),
+                "what": "the GPU-computed FP64 truth of one sampled row against the host "
+                        "oracle's FP64 GEMM"}
+
+    aux = None
+    if world == 1 and not args.skip_aux:
+        hbm = None
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            hbm = float(json.loads(pk.read_text())["hbm_gbs"])
+        aux = aux_rooflines(torch, handle, device, split_ms_avg, n, hbm or 6650.0)
+        if hbm is None:
+            aux["peak_source"] = "fallback 6650 GB/s"
+
+    del a, b, c, c0
+    torch.cuda.empty_cache()
+    batch = None
+    if not args.skip_batch:
+        batch = batch_sharded_block(torch, dist, device, sharded, rank, world)
+    kstatus = kstatus or handle.kernel_status()
 
     if rank == 0:
         line = {
@@ -358,7 +670,8 @@ def run_ours(args, rank, local_rank, world):
                        f"{m * n_local * 4 / 2**20:.0f} MiB per GPU against a 126 MB L2; "
                        "no explicit flush"),
             },
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "roofline": roofline, "rel_err": rel_err, "aux_roofline": aux, "batch_sharded": batch,
+            "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": 2 * args.steps * (2 if mode == api.ComputeMode.AUTO else 1),
             "kernel_status": kstatus, "clocks": clocks,
         }
@@ -367,6 +680,9 @@ def run_ours(args, rank, local_rank, world):
         dist.barrier()
         dist.destroy_process_group()
     handle.destroy()
+    if rel_err is not None and not rel_err["passed"]:
+        raise SystemExit(f"accuracy check failed: residual {rel_err['residual']:.3e} >= "
+                         f"threshold {rel_err['threshold']:.3e}")
 
 
 def run_sweep(args):
@@ -523,6 +839,9 @@ def main():
     ap.add_argument("--beta", type=float, default=0.5)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-check", action="store_true", help="leave the accuracy block out")
+    ap.add_argument("--skip-aux", action="store_true", help="leave the helper bandwidths out")
+    ap.add_argument("--skip-batch", action="store_true", help="leave the batch-sharded block out")
     ap.add_argument("--sweep-large", action="store_true",
                     help="with --sweep: also the 8 x 8192^3 batch and the 65536 x 65536 x 8192 GEMM")
     ap.add_argument("--sweep", action="store_true",

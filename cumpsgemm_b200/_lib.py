@@ -89,6 +89,7 @@ PROTOTYPES = {
     "cuMpSGEMM_selftest_bounded_wait": (i32, [vp, u32, C.POINTER(C.c_double)]),
     "cuMpSGEMM_set_workspace_limit": (None, [vp, C.c_size_t]),
     "cuMpSGEMM_set_count_tail_padding": (None, [vp, i32]),
+    "cuMpSGEMM_reload_tuning_env": (None, [vp]),
     "cuMpSGEMM_set_debug_buffer": (None, [vp, vp]),
     "cuMpSGEMM_set_kernel_timing": (None, [vp, i32]),
     "cuMpSGEMM_get_kernel_timing": (C.c_ulonglong, [vp, C.POINTER(C.c_double),

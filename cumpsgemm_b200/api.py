@@ -219,6 +219,11 @@ class Handle:
     def set_workspace_limit(self, nbytes: int) -> None:
         self._lib.cuMpSGEMM_set_workspace_limit(self._h, nbytes)
 
+    def reload_tuning_env(self) -> None:
+        """Read the CUMPSGEMM_TILE_N / PAIR / DRAIN_CHUNK / FIRST_CHUNK / PACE / FUSED variables
+        again (a handle reads them once, at creation)."""
+        self._lib.cuMpSGEMM_reload_tuning_env(self._h)
+
     def set_count_tail_padding(self, enable: bool) -> None:
         """Count the zeros the reference appends to matrices whose element count is not a
         multiple of 4 (src/exp_stats.cu:101-116); off by default."""
@@ -447,6 +452,15 @@ class HostGemm:
         self._bufs = {}
         self._streams = None
 
+    def adopt_staging(self, A=None, B=None, C=None) -> None:
+        """Use caller-owned device tensors as the staging buffers of A, B and C (same element
+        count and dtype as the host operands passed to `gemm` later) instead of allocating
+        new ones, e.g. buffers that already exist for a device-resident run of the same
+        problem."""
+        for key, t in (("A", A), ("B", B), ("C", C)):
+            if t is not None:
+                self._bufs[key] = t.reshape(-1)
+
     def _staging(self, key, host_tensor):
         t = self._bufs.get(key)
         if t is None or t.numel() != host_tensor.numel() or t.dtype != host_tensor.dtype:
@@ -454,20 +468,31 @@ class HostGemm:
             self._bufs[key] = t
         return t
 
-    def gemm(self, op_A, op_B, m, n, k, alpha, A_host, lda, B_host, ldb, beta, C_host, ldc, mode):
-        """Returns (bytes copied host->device, bytes copied device->host)."""
+    def gemm(self, op_A, op_B, m, n, k, alpha, A_host, lda, B_host, ldb, beta, C_host, ldc, mode,
+             A_device=None, A_ready=None):
+        """Returns (bytes copied host->device, bytes copied device->host).
+
+        A_device: A is already (or is being made) resident in this device tensor, e.g. because
+        another rank uploaded it and it arrives over NVLink; A_host is then ignored and not
+        counted.  A_ready: event after which A_device holds the data; the uploads of B and C
+        do not wait for it, only the GEMMs do."""
         torch = self.torch
-        dA = self._staging("A", A_host)
+        dA = A_device.reshape(-1) if A_device is not None else self._staging("A", A_host)
         dB = self._staging("B", B_host)
         dC = self._staging("C", C_host)
-        a_flat, b_flat, c_flat = A_host.reshape(-1), B_host.reshape(-1), C_host.reshape(-1)
+        b_flat, c_flat = B_host.reshape(-1), C_host.reshape(-1)
+        a_flat = None if A_device is not None else A_host.reshape(-1)
         need_c = complex(beta) != 0
-        es = A_host.element_size()
-        h2d = (a_flat.numel() + b_flat.numel() + (c_flat.numel() if need_c else 0)) * es
+        es = B_host.element_size()
+        h2d = ((a_flat.numel() if a_flat is not None else 0) + b_flat.numel() +
+               (c_flat.numel() if need_c else 0)) * es
         d2h = c_flat.numel() * es
         blocks = self.column_blocks if (op_B == CUBLAS_OP_N and n >= 2 * self.column_blocks) else 1
         if blocks == 1:
-            dA.copy_(a_flat, non_blocking=True)
+            if a_flat is not None:
+                dA.copy_(a_flat, non_blocking=True)
+            elif A_ready is not None:
+                torch.cuda.current_stream(self.device).wait_event(A_ready)
             dB.copy_(b_flat, non_blocking=True)
             if need_c:
                 dC.copy_(c_flat, non_blocking=True)
@@ -486,8 +511,11 @@ class HostGemm:
         for st in (s_in, s_run, s_out):
             st.wait_event(start)
         self.handle.set_stream(s_run)
-        with torch.cuda.stream(s_in):
-            dA.copy_(a_flat, non_blocking=True)
+        if a_flat is not None:
+            with torch.cuda.stream(s_in):
+                dA.copy_(a_flat, non_blocking=True)
+        elif A_ready is not None:
+            s_run.wait_event(A_ready)
         per = -(-n // blocks)
         for j0 in range(0, n, per):
             j1 = min(n, j0 + per)

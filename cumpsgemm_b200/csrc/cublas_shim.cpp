@@ -271,6 +271,9 @@ cublasStatus_t hijack_core(const char *func_name, cublasHandle_t cublas_handle,
   const cuMpSGEMM_compute_mode_t mode = cuMpSGEMM_get_compute_mode_internal(
       func_name, cublas_handle, op_A, op_B, static_cast<unsigned>(m), static_cast<unsigned>(n),
       static_cast<unsigned>(k));
+  // One handle per device serves every caller: a call owns it from here to its last launch.
+  // Calls on different streams are ordered on the device by cuMpSGEMM_set_stream.
+  std::lock_guard<std::mutex> call_lock(h->call_mutex);
 
   const bool dynamic = (g_hijack_mode == HijackMode::dynamic_mode);
   log_info(std::string(func_name) + " op=(" + op_str(op_A) + ", " + op_str(op_B) + "), shape=(" +
@@ -425,6 +428,7 @@ cublasStatus_t hijack_batched_core(const char *func_name, cublasHandle_t cublas_
   const cuMpSGEMM_compute_mode_t mode = cuMpSGEMM_get_compute_mode_internal(
       func_name, cublas_handle, op_A, op_B, static_cast<unsigned>(m), static_cast<unsigned>(n),
       static_cast<unsigned>(k));
+  std::lock_guard<std::mutex> call_lock(h->call_mutex);
   const bool dynamic = (g_hijack_mode == HijackMode::dynamic_mode);
   log_info(std::string(func_name) + " op=(" + op_str(op_A) + ", " + op_str(op_B) + "), shape=(" +
            std::to_string(m) + ", " + std::to_string(n) + ", " + std::to_string(k) +

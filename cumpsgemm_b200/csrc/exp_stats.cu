@@ -686,6 +686,7 @@ unsigned exp_stats_ext(cuMpSGEMM_handle_t handle, const unsigned m, const unsign
   if (!handle->exp_stats.profiling_enabled) {
     // two launches; the five separate ones below exist for the named timers of the profiler
     exp_stats_fused<T>(handle, id, m, n, ptr, ld, batch_size, stride);
+    mark_stream_work(handle);
     return id;
   }
   {
@@ -727,6 +728,7 @@ unsigned exp_max_ext(cuMpSGEMM_handle_t handle, const unsigned m, const unsigned
     exp_max_fused<T>(handle, id, m, n, ptr, ld, batch_size, stride);
   else
     exp_max_only<T>(handle, id, m, n, ptr, ld, batch_size, stride);
+  mark_stream_work(handle);
   return id;
 }
 template unsigned exp_max_ext<float>(cuMpSGEMM_handle_t, const unsigned, const unsigned,

@@ -219,6 +219,8 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t h, size_t bytes) {
   h->workspace_limit_bytes = bytes;
 }
 
+void cuMpSGEMM_reload_tuning_env(cuMpSGEMM_handle_t h) { h->tuning = read_tuning_env(); }
+
 void cuMpSGEMM_set_count_tail_padding(cuMpSGEMM_handle_t h, int enable) {
   h->exp_stats.count_tail_padding = (enable != 0);
 }

@@ -66,23 +66,15 @@ template <> struct Scalar<cuComplex> {
 // The pair kernel wins once there is more than one wave of pair tiles; below that the widest
 // single-CTA tile that still gives about two thirds of the SMs a tile is fastest: narrower
 // tiles move the same operand bytes for fewer MMAs.
-struct TileChoice {
-  int tile_n;
-  bool pair;
-};
+} // namespace
 
-TileChoice pick_tile(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64_t n,
+TileChoice pick_tile(const Tuning &tuning, unsigned num_sms, std::uint64_t m_exp, std::uint64_t n,
                      std::uint64_t batch, bool ec) {
-  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
-  const bool pair_off = pair_env != nullptr && pair_env[0] == '0';
-  const bool pair_on = pair_env != nullptr && pair_env[0] == '1';
-  const char *force = std::getenv("CUMPSGEMM_TILE_N");
-  if (force != nullptr) {
-    const int v = std::atoi(force);
-    if (v == 256) return {256, ec && !pair_off};
-    if (v == 128 || v == 64) return {v, false};
-  }
-  const std::uint64_t sms = static_cast<std::uint64_t>(h->num_sms);
+  const bool pair_off = tuning.pair == 0;
+  const bool pair_on = tuning.pair == 1;
+  if (tuning.tile_n == 256) return {256, ec && !pair_off};
+  if (tuning.tile_n == 128 || tuning.tile_n == 64) return {tuning.tile_n, false};
+  const std::uint64_t sms = static_cast<std::uint64_t>(num_sms);
   const std::uint64_t pair_tiles = ((m_exp + 255) / 256) * ((n + 255) / 256) * batch;
   const std::uint64_t tiles_256 = ((m_exp + 127) / 128) * ((n + 255) / 256) * batch;
   const std::uint64_t tiles_128 = ((m_exp + 127) / 128) * ((n + 127) / 128) * batch;
@@ -91,8 +83,6 @@ TileChoice pick_tile(const cuMpSGEMM_handle *h, std::uint64_t m_exp, std::uint64
   if (3 * tiles_128 >= 2 * sms) return {128, false};
   return {64, false};
 }
-
-} // namespace
 
 template <class T>
 cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperation_t op_B,
@@ -155,7 +145,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   const std::uint64_t fpe = is_complex ? 2 : 1;
   const std::uint64_t m_exp = m * fpe; // rows of the expanded real problem
   const std::uint64_t k_exp = k * fpe;
-  const TileChoice choice = pick_tile(h, m_exp, n, batch, ec);
+  const TileChoice choice = pick_tile(h->tuning, h->num_sms, m_exp, n, batch, ec);
   const int tile_n = choice.tile_n;
   const bool use_pair = choice.pair;
   if (used_kernel_module_id != nullptr)
@@ -253,6 +243,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       g.dev_status = h->dev_status;
       g.wave_counter = reinterpret_cast<unsigned int *>(h->dev_status + 1);
       g.debug = h->debug_buffer;
+      g.tuning = h->tuning;
       err = use_pair ? launch_tcec_gemm_pair(g, h->cuda_stream)
                      : launch_tcec_gemm(g, h->cuda_stream);
       if (h->kernel_timing) {
@@ -262,6 +253,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
     }
   }
   if (prof) h->exp_stats.profiler.stop("gemm_kernel", h->cuda_stream);
+  mark_stream_work(h);
   if (err != cudaSuccess) {
     log_error(std::string("kernel launch failed: ") + cudaGetErrorString(err));
     return CUBLAS_STATUS_EXECUTION_FAILED;

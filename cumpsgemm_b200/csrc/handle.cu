@@ -28,6 +28,23 @@ void log_error(const std::string &s) {
     std::fflush(stdout);
   }
 }
+Tuning read_tuning_env() {
+  Tuning t;
+  auto as_int = [](const char *name, int dflt) {
+    const char *e = std::getenv(name);
+    return (e != nullptr && e[0] != '\0') ? std::atoi(e) : dflt;
+  };
+  const int tn = as_int("CUMPSGEMM_TILE_N", 0);
+  t.tile_n = (tn == 256 || tn == 128 || tn == 64) ? tn : 0;
+  const int pr = as_int("CUMPSGEMM_PAIR", -1);
+  t.pair = (pr == 0 || pr == 1) ? pr : -1;
+  t.drain_chunk = as_int("CUMPSGEMM_DRAIN_CHUNK", 0);
+  t.first_chunk = as_int("CUMPSGEMM_FIRST_CHUNK", 0);
+  t.pace = as_int("CUMPSGEMM_PACE", 1) != 0 ? 1 : 0;
+  const int fu = as_int("CUMPSGEMM_FUSED", -1);
+  t.fused = (fu == 0 || fu == 1) ? fu : -1;
+  return t;
+}
 void log_warning(const std::string &s) {
   if (env_flag("CUMPSGEMM_ERROR_LOG", false)) {
     std::fprintf(stdout, "[cuMpSGEMM WARNING] %s\n", s.c_str());
@@ -70,6 +87,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
         cudaSuccess;
   ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
   ok &= cudaMalloc(&h->dev_status, 2 * sizeof(int)) == cudaSuccess; // status, wave counter
+  ok &= cudaEventCreateWithFlags(&h->order_event, cudaEventDisableTiming) == cudaSuccess;
   const size_t scan_scratch_bytes = static_cast<size_t>(h->num_sms) * 8 * 24 * 2 + 16;
   ok &= cudaMalloc(&es.dev_scan_scratch, scan_scratch_bytes) == cudaSuccess;
   if (!ok) {
@@ -92,6 +110,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
     return CUBLAS_STATUS_EXECUTION_FAILED;
   }
   h->exp_stats.count_tail_padding = env_flag("CUMPSGEMM_COUNT_TAIL_PADDING", false);
+  h->tuning = read_tuning_env();
   const char *ws_env = std::getenv("CUMPSGEMM_WORKSPACE_LIMIT_MB");
   if (ws_env != nullptr) h->workspace_limit_bytes = std::strtoull(ws_env, nullptr, 10) << 20;
   *handle = h;
@@ -110,6 +129,7 @@ extern "C" cublasStatus_t cuMpSGEMM_destroy(cuMpSGEMM_handle_t handle) {
   cudaFree(handle->dev_dyn_params);
   cudaFree(handle->dev_status);
   cudaFree(handle->workspace);
+  if (handle->order_event != nullptr) cudaEventDestroy(handle->order_event);
   delete handle;
   return CUBLAS_STATUS_SUCCESS;
 }
@@ -117,6 +137,21 @@ extern "C" cublasStatus_t cuMpSGEMM_destroy(cuMpSGEMM_handle_t handle) {
 extern "C" cublasStatus_t cuMpSGEMM_set_stream(cuMpSGEMM_handle_t handle,
                                                const cudaStream_t cuda_stream) {
   if (handle == nullptr) return CUBLAS_STATUS_NOT_INITIALIZED;
+  if (cuda_stream != handle->cuda_stream && handle->order_event_recorded) {
+    // Work already enqueued through this handle may still use its workspace, rings and
+    // counters: whatever runs on the new stream is ordered behind it.  (The reference has one
+    // stream per handle at a time and no such hazard, src/handle.cu:48-52, because its kernels
+    // keep no operand workspace.)
+    DeviceGuard guard(handle->device);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(cuda_stream, &cap) == cudaSuccess &&
+        cap == cudaStreamCaptureStatusNone) {
+      if (cudaStreamWaitEvent(cuda_stream, handle->order_event, 0) != cudaSuccess)
+        cudaGetLastError();
+    } else {
+      cudaGetLastError();
+    }
+  }
   handle->cuda_stream = cuda_stream;
   return CUBLAS_STATUS_SUCCESS;
 }

@@ -4,6 +4,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <string>
 #include <unordered_map>
 #include <utility>
@@ -65,6 +66,23 @@ struct Profiler {
   ~Profiler();
 };
 
+// Tuning switches read from the environment.  A handle reads them once, when it is created
+// (cuMpSGEMM_reload_tuning_env reads them again); entry points without a handle read them per
+// call.  CUMPSGEMM_TILE_N = 256 / 128 / 64 forces the tile width, CUMPSGEMM_PAIR = 0 / 1 the
+// CTA-pair kernel off / on, CUMPSGEMM_DRAIN_CHUNK and CUMPSGEMM_FIRST_CHUNK the number of
+// K stages per accumulator drain (pair kernel), CUMPSGEMM_PACE = 0 the wave pacing off,
+// CUMPSGEMM_FUSED = 0 / 1 the kernel that splits operands on the fly off / on wherever it is
+// applicable.
+struct Tuning {
+  int tile_n = 0;      // 0 = by rule
+  int pair = -1;       // -1 = by rule
+  int drain_chunk = 0; // 0 = default
+  int first_chunk = 0; // 0 = default
+  int pace = 1;
+  int fused = -1;      // -1 = by rule
+};
+Tuning read_tuning_env();
+
 struct ExpStatsState {
   bool enabled = false;
   unsigned long long *dev_total = nullptr;
@@ -115,6 +133,8 @@ struct cuMpSGEMM_handle {
   std::size_t workspace_bytes = 0;
   std::size_t workspace_limit_bytes = 0; // 0 = derive from free memory
 
+  cumpsgemm_b200::Tuning tuning;
+
   // Device status word the GEMM kernel writes when a bounded wait gives up.
   int *dev_status = nullptr; // [0] kernel status word, [1] wave counter of the pair kernel
 
@@ -125,10 +145,39 @@ struct cuMpSGEMM_handle {
   };
   bool kernel_timing = false;
   unsigned long long *debug_buffer = nullptr; // caller-owned, see cuMpSGEMM_set_debug_buffer
+
+  // The workspace, the DynParams ring, the statistics scratch and the wave counter are shared by
+  // all calls on the handle.  Calls on one stream are ordered by the stream; when the handle is
+  // moved to another stream (cuMpSGEMM_set_stream; the interception layer does it for every
+  // caller's cuBLAS stream) the new stream first waits for `order_event`, which every call that
+  // touches the shared buffers records behind its last launch.
+  cudaEvent_t order_event = nullptr;
+  bool order_event_recorded = false;
+  // Held by the interception layer from set_stream to the last launch of a call, so that host
+  // threads sharing the per-device handle cannot interleave inside a call.  Users of the handle
+  // API use one handle per thread (or their own lock), as with cuBLAS handles.
+  std::mutex call_mutex;
   std::vector<TimingTriple> timing_events;
 };
 
 namespace cumpsgemm_b200 {
+
+// Record the handle's ordering event behind the work just enqueued (see cuMpSGEMM_handle).
+// Skipped while the stream is being captured into a graph: a captured event cannot order
+// work outside the capture, and a graph replays as one unit of its launch stream anyway.
+inline void mark_stream_work(cuMpSGEMM_handle *h) {
+  if (h->order_event == nullptr) return;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(h->cuda_stream, &cap) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  if (cap != cudaStreamCaptureStatusNone) return;
+  if (cudaEventRecord(h->order_event, h->cuda_stream) == cudaSuccess)
+    h->order_event_recorded = true;
+  else
+    cudaGetLastError();
+}
 
 // RAII: make the handle's device current for the duration of a call.
 struct DeviceGuard {
@@ -195,6 +244,7 @@ struct TcecGemmArgs {
   // Optional device word the persistent pair kernel uses to keep its clusters in step
   // (zeroed by the launcher before every launch); null switches the pacing off.
   unsigned int *wave_counter = nullptr;
+  Tuning tuning;
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
 // Self-test of the bounded mbarrier wait (see cuMpSGEMM_selftest_bounded_wait).
@@ -251,6 +301,16 @@ cublasStatus_t tiny_gemm(cuMpSGEMM_handle *h, bool long_is_m, cublasOperation_t 
                          std::uint64_t stride_c, std::uint64_t batch);
 
 // ---------------------------------------------------------------- GEMM dispatch
+// Tile for a problem: width 256 / 128 / 64 of the single-CTA kernel (128 rows), or the CTA-pair
+// kernel's 256 x 256 tile (error-corrected modes only).  m_exp = rows of the real problem
+// (twice m for complex).  The one rule every entry point uses.
+struct TileChoice {
+  int tile_n;
+  bool pair;
+};
+TileChoice pick_tile(const Tuning &tuning, unsigned num_sms, std::uint64_t m_exp, std::uint64_t n,
+                     std::uint64_t batch, bool error_correction);
+
 // Shared implementation behind gemm<T> / gemm_stridedBatch<T>.
 // `dyn` != nullptr selects the fused scaling path (scale in the split pass,
 // un-scale in the epilogue); `gate_by_flag` launches both kinds gated on

@@ -12,10 +12,14 @@
 // Limits and rules for the caller:
 //   * The array is kStaticScratchBytes (32 MiB) per GPU, resident from library load to
 //     process exit on every GPU that loads the library.  The panels of a call need
-//     planes * (round_up(m,128) + round_up(n,tile)) * round_up(k,64) * elem bytes
-//     (planes = 2, elem = 2 for FP16TCEC, 4 for TF32TCEC); e.g. FP16TCEC m=n=k=2048 fits
-//     exactly.  Larger problems are rejected with CUBLAS_STATUS_INVALID_VALUE and an error
-//     line; nothing is launched.
+//     2 * (round_up(m, tile_m) + round_up(n, tile_n)) * round_up(k,64) * elem bytes
+//     (elem = 2 for FP16TCEC, 4 for TF32TCEC; tile_m x tile_n is the tile the library's one
+//     tile rule picks for the shape: 256 x 256 when the CTA-pair kernel runs, else 128 x
+//     256 / 128 / 64; the environment overrides CUMPSGEMM_TILE_N and CUMPSGEMM_PAIR apply
+//     here as everywhere).  The bound that holds for every tile choice is
+//     2 * (round_up(m,256) + round_up(n,256)) * round_up(k,64) * elem <= 32 MiB; e.g.
+//     FP16TCEC m=n=k=2048 fits exactly.  Larger problems are rejected with
+//     CUBLAS_STATUS_INVALID_VALUE and an error line; nothing is launched.
 //   * The first call on each device looks up the device address of the array
 //     (cudaGetSymbolAddress) and sets the kernels' shared-memory attribute.  Make that first
 //     call before starting any stream capture on that device.
@@ -66,20 +70,6 @@ cudaError_t setup_device(int dev, PerDevice **out) {
   return cudaSuccess;
 }
 
-// Same rule as the regular dispatch so both entry points run the same tile configuration.
-int pick_tile(int num_sms, std::uint64_t m, std::uint64_t n) {
-  const char *force = std::getenv("CUMPSGEMM_TILE_N");
-  if (force != nullptr) {
-    const int v = std::atoi(force);
-    if (v == 256 || v == 128 || v == 64) return v;
-  }
-  const std::uint64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-  if (3 * pair_tiles >= static_cast<std::uint64_t>(num_sms)) return 256;
-  const std::uint64_t tiles_128 = ((m + 127) / 128) * ((n + 127) / 128);
-  if (tiles_128 >= static_cast<std::uint64_t>(num_sms)) return 128;
-  return 64;
-}
-
 } // namespace
 
 using namespace cumpsgemm_b200;
@@ -113,20 +103,28 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
 
   const SplitKind kind = (compute_mode == CUMPSGEMM_FP16TCEC) ? SplitKind::fp16 : SplitKind::tf32;
   const std::size_t es = (kind == SplitKind::fp16) ? 2 : 4;
-  const int tile_n = pick_tile(pd->num_sms, m, n);
-  const char *pair_env = std::getenv("CUMPSGEMM_PAIR");
-  const bool use_pair = tile_n == 256 && !(pair_env != nullptr && pair_env[0] == '0');
+  // the tile rule of the regular entry points, so that both run the same kernels
+  const Tuning tuning = read_tuning_env(); // no handle to cache them in
+  const TileChoice choice = pick_tile(tuning, static_cast<unsigned>(pd->num_sms), m, n, 1, true);
+  const int tile_n = choice.tile_n;
+  const bool use_pair = choice.pair;
   const std::uint64_t rows_pad_a = round_up(m, use_pair ? 256 : 128);
   const std::uint64_t rows_pad_b = round_up(n, tile_n);
   const std::uint64_t k_pad = round_up(k, 64);
-  const std::uint64_t bytes_a = 2 * rows_pad_a * k_pad * es;
-  const std::uint64_t bytes_b = 2 * rows_pad_b * k_pad * es;
-  if (bytes_a + bytes_b > kStaticScratchBytes) {
+  // Each factor is below 2^31, so the row sum times k_pad stays below 2^63 / 8 only after this
+  // first test; the byte counts are formed afterwards and cannot wrap.
+  const std::uint64_t max_elems = kStaticScratchBytes / (2 * es);
+  const bool fits = (rows_pad_a + rows_pad_b) <= max_elems && k_pad <= max_elems &&
+                    (rows_pad_a + rows_pad_b) * k_pad <= max_elems;
+  const std::uint64_t bytes_a = fits ? 2 * rows_pad_a * k_pad * es : 0;
+  const std::uint64_t bytes_b = fits ? 2 * rows_pad_b * k_pad * es : 0;
+  if (!fits) {
     log_error("cuMpSGEMM_sgemm_static_scratch: m=" + std::to_string(m) + " n=" +
-              std::to_string(n) + " k=" + std::to_string(k) + " needs " +
-              std::to_string(bytes_a + bytes_b) + " bytes of operand panels; the built-in " +
-              "scratch array holds " + std::to_string(kStaticScratchBytes) +
-              " bytes. Use cuMpSGEMM_sgemm for this size.");
+              std::to_string(n) + " k=" + std::to_string(k) + " needs 2 * (" +
+              std::to_string(rows_pad_a) + " + " + std::to_string(rows_pad_b) + ") * " +
+              std::to_string(k_pad) + " * " + std::to_string(es) +
+              " bytes of operand panels; the built-in scratch array holds " +
+              std::to_string(kStaticScratchBytes) + " bytes. Use cuMpSGEMM_sgemm for this size.");
     return CUBLAS_STATUS_INVALID_VALUE;
   }
   unsigned char *panel_a = static_cast<unsigned char *>(pd->scratch);
@@ -184,6 +182,7 @@ extern "C" cublasStatus_t cuMpSGEMM_sgemm_static_scratch(
     g.dyn = nullptr;
     g.tile_n = tile_n;
     g.dev_status = nullptr; // no handle, hence no status word; waits stay bounded
+    g.tuning = tuning;
     err = use_pair ? launch_tcec_gemm_pair(g, stream) : launch_tcec_gemm(g, stream);
   }
   if (err != cudaSuccess) {

@@ -370,15 +370,16 @@ template <int KIND, int BN, bool EC>
 cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   using Cfg = TileCfg<BN, EC>;
   auto kernel = tcec_gemm_kernel<KIND, BN, EC>;
-  static bool attr_set[64] = {};
+  static std::once_flag once[64];
+  static cudaError_t setup_error[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [&]() {
+    setup_error[dev] = cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+  });
+  if (setup_error[dev] != cudaSuccess) return setup_error[dev];
   const uint32_t planes = a.batch * (EC ? 2u : 1u);
   CUtensorMap map_a, map_b;
   if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, BM) ||

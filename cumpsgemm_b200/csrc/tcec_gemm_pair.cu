@@ -32,6 +32,8 @@
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 
+#include <mutex>
+
 namespace cumpsgemm_b200 {
 namespace {
 
@@ -411,15 +413,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 
 template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
   auto kernel = tcec_gemm_pair_kernel<KIND>;
-  static bool attr_set[64] = {};
-  static int max_clusters[64] = {};
+  // per device, once (any thread): shared-memory attribute and the number of co-resident clusters
+  static std::once_flag once[64];
+  static cudaError_t setup_error[64];
+  static int max_clusters[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!attr_set[dev]) {
-    cudaError_t e =
+  std::call_once(once[dev], [&]() {
+    setup_error[dev] =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return e;
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // one cluster per SM pair; if the device can co-schedule fewer, use what it reports
@@ -429,14 +432,15 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     int active = 0;
-    if (cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) == cudaSuccess) {
+    if (setup_error[dev] == cudaSuccess &&
+        cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) == cudaSuccess) {
       if (active > 0 && active < clusters) clusters = active;
     } else {
       cudaGetLastError();
     }
     max_clusters[dev] = clusters > 0 ? clusters : 1;
-    attr_set[dev] = true;
-  }
+  });
+  if (setup_error[dev] != cudaSuccess) return setup_error[dev];
   const uint32_t planes = a.batch * 2u;
   CUtensorMap map_a, map_b;
   if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, 128) ||
@@ -464,8 +468,7 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   p.status = a.dev_status;
   p.debug = a.debug;
   {
-    const char *e = std::getenv("CUMPSGEMM_DRAIN_CHUNK");
-    const int v = (e != nullptr) ? std::atoi(e) : 0;
+    const int v = a.tuning.drain_chunk;
     // Default: two stages (128 FP16 / 64 TF32 k values) per drain.  Measured at m=n=k=16384,
     // uniform(-1,1): residual 3.1e-7 / 2.8e-7 / 3.7e-7 / 6.5e-7 / 2.5e-6 / 1.9e-5 for 1 / 2 / 4 /
     // 8 / 32 / 256 stages per drain (FP32 cuBLAS SGEMM on the same inputs: 2.3e-6).
@@ -485,8 +488,7 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     const uint32_t k_total = p.k_blocks * k_per_stage;
     uint32_t first_k = (k_total >= 8192u) ? 512u : (k_total >= 2048u ? 256u : 128u);
     if (a.kind != SplitKind::fp16) first_k /= 2u;
-    const char *f = std::getenv("CUMPSGEMM_FIRST_CHUNK");
-    const int fv = (f != nullptr) ? std::atoi(f) : 0;
+    const int fv = a.tuning.first_chunk;
     p.first_chunk = (fv >= 1) ? static_cast<uint32_t>(fv) : first_k / k_per_stage;
     if (p.first_chunk < p.drain_chunk) p.first_chunk = p.drain_chunk;
   }
@@ -501,8 +503,7 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   // Pacing pays when tiles are long (the drift it removes is 2 % of a tile) and clusters share
   // panel rows; for short tiles a barrier per tile costs more than it saves.
   if (a.wave_counter != nullptr && total > clusters && p.k_blocks >= kPaceMinStages) {
-    const char *e = std::getenv("CUMPSGEMM_PACE");
-    if (e == nullptr || std::atoi(e) != 0) {
+    if (a.tuning.pace != 0) {
       const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
       if (me != cudaSuccess) return me;
       p.wave_counter = a.wave_counter;

@@ -143,6 +143,10 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
  * when 0 is below the stage's threshold), so counts and decisions equal the reference's for
  * such shapes too; with it off only real matrix elements are counted. */
 void cuMpSGEMM_set_count_tail_padding(cuMpSGEMM_handle_t handle, int enable);
+/* A handle reads the tuning variables (CUMPSGEMM_TILE_N, CUMPSGEMM_PAIR, CUMPSGEMM_DRAIN_CHUNK,
+ * CUMPSGEMM_FIRST_CHUNK, CUMPSGEMM_PACE, CUMPSGEMM_FUSED) once, when it is created, so that a
+ * GEMM call does not query the environment; this reads them again. */
+void cuMpSGEMM_reload_tuning_env(cuMpSGEMM_handle_t handle);
 /* Per-launch device timing with CUDA events on the handle's stream (off by default).  While
  * enabled every split + GEMM launch group records three events; get_kernel_timing
  * synchronises the stream, returns the number of launch groups since the last query and the
@@ -268,9 +272,13 @@ cublasStatus_t cuMpSGEMM_cgemm_2xNx2(cuMpSGEMM_handle_t handle, cublasOperation_
  * cuMpSGEMM_sgemm in FP16TCEC or TF32TCEC mode, but the split operand panels live in a 32 MiB
  * array built into the library instead of a workspace obtained with cudaMalloc, and no handle
  * is needed.  The call issues kernel launches on `stream` and nothing else.
- *   - Problems whose panels exceed 32 MiB (FP16TCEC: 4*(round_up(m,128)+round_up(n,tile))*
- *     round_up(k,64) bytes, twice that for TF32TCEC; m=n=k=2048 FP16TCEC just fits) return
- *     CUBLAS_STATUS_INVALID_VALUE with an error line and launch nothing.
+ *   - Problems whose panels exceed 32 MiB return CUBLAS_STATUS_INVALID_VALUE with an error
+ *     line and launch nothing.  FP16TCEC panels take 4*(round_up(m,tile_m)+round_up(n,tile_n))*
+ *     round_up(k,64) bytes, TF32TCEC twice that, where tile_m x tile_n is the tile the library
+ *     picks for the shape (256 x 256 with the CTA-pair kernel, else 128 x 256/128/64; the
+ *     CUMPSGEMM_TILE_N / CUMPSGEMM_PAIR overrides count).  Whatever the tile,
+ *     4*(round_up(m,256)+round_up(n,256))*round_up(k,64) <= 32 MiB always fits (FP16TCEC;
+ *     m=n=k=2048 fits exactly).
  *   - The first call on a device resolves the array's device address and configures the
  *     kernels; issue it before any stream capture on that device.
  *   - The array is shared by all calls on a GPU: calls that overlap in time on one GPU race.

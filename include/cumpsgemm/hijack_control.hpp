@@ -17,7 +17,9 @@ cuMpSGEMM_handle_t get_internal_global_handle();
 // Force one mode for every intercepted call / go back to the rule chain.
 void set_compute_mode(const cuMpSGEMM_compute_mode_t mode);
 void unset_compute_mode();
-// Accepted for source compatibility; tiny (M,2,2) GEMMs take the normal path.
+// Route intercepted (M,2,2) / (2,N,2) GEMMs with a power-of-two long side to the library's own
+// FP32 streaming kernels (the reference calls the cuGEMM-Mx2x2 library there,
+// src/cumpsgemm_cublas.cu:269-338).
 void enable_custom_gemm_Mx2x2();
 void disable_custom_gemm_Mx2x2();
 

@@ -110,6 +110,7 @@ def test_every_tile_width(handle, oracle, tile):
         tile = 256
         os.environ["CUMPSGEMM_PAIR"] = "0"
     os.environ["CUMPSGEMM_TILE_N"] = str(tile)
+    handle.reload_tuning_env()
     try:
         m, n, k = 384, 520, 200
         _, _, _, res, truth, _ = _run_real(handle, oracle, N, N, m, n, k, FP16TCEC, beta=0.5, seed=5)
@@ -219,6 +220,7 @@ def test_pair_kernel_ragged_multiwave_batched(handle, oracle, mode):
     batch, m, n, k = 4, 612, 2381, 2088          # 3 x 10 pair tiles per entry: 120 on 74 slots
     os.environ["CUMPSGEMM_TILE_N"] = "256"       # force the pair kernel whatever the tile rule says
     os.environ["CUMPSGEMM_PAIR"] = "1"
+    handle.reload_tuning_env()
     try:
         lda, ldb, ldc = m + 4, k + 8, m + 12
         sa, sb, sc = lda * k + 16, ldb * n + 4, ldc * n
@@ -342,6 +344,7 @@ def test_scheduling_aids_do_not_change_results(handle, oracle):
     try:
         for pace in ("1", "0", "1"):
             os.environ["CUMPSGEMM_PACE"] = pace
+            handle.reload_tuning_env()
             c = c0.clone()
             handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c, m, FP16TCEC)
             outs.append(c)

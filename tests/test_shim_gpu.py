@@ -318,3 +318,40 @@ def test_pytorch_under_ld_preload():
     for tag in ("RES_S", "RES_C", "RES_B"):
         val = float(re.search(tag + r" (\S+)", out).group(1))
         assert val < 2.0 ** -23 * np.sqrt(1280), (tag, val)
+
+
+def test_two_streams_share_the_per_device_handle(oracle):
+    """An application that runs GEMMs on two streams of one GPU: both reach the one handle the
+    interception layer keeps per device, whose operand workspace and rings are shared.  The
+    calls are interleaved with no host synchronisation in between; each stream's result must
+    be the product of its own operands."""
+    torch, lib = _setup()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    with torch.cuda.stream(s1):
+        blas1 = torch.cuda.current_blas_handle()
+    with torch.cuda.stream(s2):
+        blas2 = torch.cuda.current_blas_handle()
+    shapes = ((1536, 1280, 2048), (640, 900, 1100))
+    ops = []
+    for i, (m, n, k) in enumerate(shapes):
+        a, b = oracle.gen_uniform(40 + i, m * k), oracle.gen_uniform(50 + i, k * n)
+        ops.append((m, n, k, a, b, torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(),
+                    torch.zeros(m * n, device="cuda")))
+    torch.cuda.synchronize()
+    alpha, beta = C.c_float(1.0), C.c_float(0.0)
+    try:
+        for mode in (1, 11):                         # FP16TCEC, FP16TCEC_SCALING
+            assert lib.cuMpSGEMM_hijack_set_compute_mode(mode) == 0
+            for (m, n, k, a, b, da, db, dc) in ops:
+                dc.zero_()
+            torch.cuda.synchronize()
+            for _ in range(12):
+                for blas, (m, n, k, a, b, da, db, dc) in zip((blas1, blas2), ops):
+                    assert lib.cublasSgemm_v2(blas, 0, 0, m, n, k, C.byref(alpha), da.data_ptr(), m,
+                                              db.data_ptr(), k, C.byref(beta), dc.data_ptr(), m) == 0
+            torch.cuda.synchronize()
+            for (m, n, k, a, b, da, db, dc) in ops:
+                truth = oracle.gemm_f64(0, 0, m, n, k, 1.0, a, m, b, k, 0.0, None, m)
+                assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    finally:
+        lib.cuMpSGEMM_hijack_unset_compute_mode()
