@@ -33,6 +33,7 @@ CUDA_SOURCES = [
     "split_kernels.cu",
     "tcec_gemm.cu",
     "tcec_gemm_pair.cu",
+    "tcec_gemm_fused.cu",
     "gemm_api.cu",
     "ext_api.cu",
     "static_scratch_gemm.cu",

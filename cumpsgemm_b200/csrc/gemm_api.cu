@@ -84,6 +84,58 @@ TileChoice pick_tile(const Tuning &tuning, unsigned num_sms, std::uint64_t m_exp
   return {64, false};
 }
 
+namespace {
+
+// The kernel that splits operands on the fly handles FP16TCEC (with or without fused scaling)
+// on 16-byte aligned strided operands in the layouts its converters know; see
+// tcec_gemm_fused.cu.  Returns false when the call has to take the pre-split path.
+template <class T>
+bool fused_args(const cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperation_t op_B,
+                std::uint64_t m, std::uint64_t n, std::uint64_t k, const T *a, std::uint64_t lda,
+                std::uint64_t stridea, const T *b, std::uint64_t ldb, std::uint64_t strideb,
+                std::uint64_t batch, FusedGemmArgs *out) {
+  constexpr bool is_complex = std::is_same<T, cuComplex>::value;
+  constexpr std::uint64_t fpe = is_complex ? 2 : 1;
+  if (h->tuning.fused == 0) return false;
+  if (batch > 0x7fffffffull) return false;
+  if (is_complex && (op_A != CUBLAS_OP_N || op_B != CUBLAS_OP_N)) return false;
+  const std::uint64_t lda_f = lda * fpe, ldb_f = ldb * fpe;
+  const std::uint64_t sa_f = (batch > 1 ? stridea : 0) * fpe, sb_f = (batch > 1 ? strideb : 0) * fpe;
+  const bool aligned = (reinterpret_cast<std::uintptr_t>(a) % 16 == 0) &&
+                       (reinterpret_cast<std::uintptr_t>(b) % 16 == 0) && lda_f % 4 == 0 &&
+                       ldb_f % 4 == 0 && sa_f % 4 == 0 && sb_f % 4 == 0;
+  if (!aligned) return false;
+  const std::uint64_t m_exp = m * fpe, k_exp = k * fpe;
+  if (h->tuning.fused != 1) {
+    // Measured crossover (B200): the on-the-fly split wins while the K loop is short enough
+    // that the split pass and its workspace traffic weigh as much as the products themselves.
+    if (k_exp > 1024) return false;
+  }
+  out->a = reinterpret_cast<const float *>(a);
+  out->b = reinterpret_cast<const float *>(b);
+  out->lda = lda_f;
+  out->ldb = ldb_f;
+  out->stride_a = sa_f;
+  out->stride_b = sb_f;
+  if (is_complex) {
+    out->layout_a = 2;
+    out->layout_b = 0;
+  } else {
+    out->layout_a = (op_A == CUBLAS_OP_N) ? 1 : 0;
+    out->layout_b = (op_B == CUBLAS_OP_N) ? 0 : 1;
+  }
+  out->m = static_cast<std::uint32_t>(m_exp);
+  out->n = static_cast<std::uint32_t>(n);
+  out->k = static_cast<std::uint32_t>(k_exp);
+  out->batch = static_cast<std::uint32_t>(batch);
+  out->is_complex = is_complex;
+  out->tile_n = (h->tuning.tile_n == 64 || n <= 64) ? 64 : 128;
+  out->tuning = h->tuning;
+  return true;
+}
+
+} // namespace
+
 template <class T>
 cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperation_t op_B,
                              std::uint64_t m, std::uint64_t n, std::uint64_t k, const T *alpha,
@@ -145,6 +197,43 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   const std::uint64_t fpe = is_complex ? 2 : 1;
   const std::uint64_t m_exp = m * fpe; // rows of the expanded real problem
   const std::uint64_t k_exp = k * fpe;
+
+  // ---- one launch, no workspace: operands split inside the GEMM kernel
+  FusedGemmArgs fa;
+  if (mode == CUMPSGEMM_FP16TCEC && !ptr_arrays &&
+      fused_args<T>(h, op_A, op_B, m, n, k, a, lda, stridea, b, ldb, strideb, batch, &fa)) {
+    fa.c = reinterpret_cast<float *>(c);
+    fa.ldc = ldc * fpe;
+    fa.stride_c = stridec * fpe;
+    fa.alpha_r = Scalar<T>::re(alpha);
+    fa.alpha_i = Scalar<T>::im(alpha);
+    fa.beta_r = Scalar<T>::re(beta);
+    fa.beta_i = Scalar<T>::im(beta);
+    fa.dyn = dyn;
+    fa.dev_status = h->dev_status;
+    if (used_kernel_module_id != nullptr) *used_kernel_module_id = (fa.tile_n == 128) ? 1u : 2u;
+    const bool prof = h->exp_stats.profiling_enabled;
+    if (prof) h->exp_stats.profiler.start("gemm_kernel", h->cuda_stream);
+    cuMpSGEMM_handle::TimingTriple tt{};
+    if (h->kernel_timing) {
+      for (auto &e : tt.e) cudaEventCreate(&e);
+      cudaEventRecord(tt.e[0], h->cuda_stream);
+      cudaEventRecord(tt.e[1], h->cuda_stream);
+    }
+    const cudaError_t ferr = launch_tcec_gemm_fused(fa, h->cuda_stream);
+    if (h->kernel_timing) {
+      cudaEventRecord(tt.e[2], h->cuda_stream);
+      h->timing_events.push_back(tt);
+    }
+    if (prof) h->exp_stats.profiler.stop("gemm_kernel", h->cuda_stream);
+    mark_stream_work(h);
+    if (ferr != cudaSuccess) {
+      log_error(std::string("kernel launch failed: ") + cudaGetErrorString(ferr));
+      return CUBLAS_STATUS_EXECUTION_FAILED;
+    }
+    return CUBLAS_STATUS_SUCCESS;
+  }
+
   const TileChoice choice = pick_tile(h->tuning, h->num_sms, m_exp, n, batch, ec);
   const int tile_n = choice.tile_n;
   const bool use_pair = choice.pair;

@@ -247,6 +247,26 @@ struct TcecGemmArgs {
   Tuning tuning;
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
+// GEMM that splits its operands on the fly (tcec_gemm_fused.cu): no workspace, FP16 kinds with
+// error correction only.  Sizes are those of the real problem (complex operands expanded:
+// m = 2 * rows of C, k = 2 * K); leading dimensions and strides are in floats.
+struct FusedGemmArgs {
+  const float *a, *b;
+  std::uint64_t lda, ldb;           // floats between consecutive columns of the stored operand
+  std::uint64_t stride_a, stride_b; // floats between batch entries
+  int layout_a, layout_b;           // 0 = K contiguous, 1 = row contiguous, 2 = complex A, op N
+  std::uint32_t m, n, k;
+  std::uint32_t batch;
+  float *c;
+  std::uint64_t ldc, stride_c; // floats
+  float alpha_r, alpha_i, beta_r, beta_i;
+  bool is_complex;
+  const DynParams *dyn; // nullable: scale factors and the un-scaling of C
+  int *dev_status;
+  int tile_n; // 128 or 64
+  Tuning tuning;
+};
+cudaError_t launch_tcec_gemm_fused(const FusedGemmArgs &a, cudaStream_t stream);
 // Self-test of the bounded mbarrier wait (see cuMpSGEMM_selftest_bounded_wait).
 cudaError_t launch_bounded_wait_selftest(int *dev_status, unsigned long long limit_ns,
                                          unsigned long long *dev_waited_ns, cudaStream_t stream);

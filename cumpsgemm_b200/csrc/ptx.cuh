@@ -31,6 +31,16 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Register re-allocation between the warpgroups of a CTA (all four warps of a warpgroup must
+// execute it; N multiple of 8 in [24, 256]).  dec returns registers to the CTA's pool, inc
+// blocks until the pool holds enough.
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -53,6 +63,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       "{\n\t"
       ".reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Non-blocking test of a phase (try_wait may suspend the thread; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(done)
@@ -88,6 +113,50 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3f) == 0) {
+      if (*abort_smem) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *abort_smem = 1;
+        if (status_gmem != nullptr) atomicCAS(status_gmem, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded wait for roles that can afford a little extra latency: between polls the thread
+// sleeps, so a waiting warp leaves the issue slots of its scheduler to the warps that work.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity,
+                                                  volatile int *abort_smem, int *status_gmem,
+                                                  int code, uint32_t sleep_ns,
+                                                  uint64_t limit_ns = kWaitLimitNs) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_smem) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *abort_smem = 1;
+        if (status_gmem != nullptr) atomicCAS(status_gmem, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Bounded wait that polls with the non-blocking test: lowest wake-up latency, for the few
+// threads whose reaction time is on the critical path of a short pipeline stage.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity,
+                                               volatile int *abort_smem, int *status_gmem,
+                                               int code, uint64_t limit_ns = kWaitLimitNs) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((++spins & 0xff) == 0) {
       if (*abort_smem) return false;
       if (globaltimer_ns() - t0 > limit_ns) {
         *abort_smem = 1;
@@ -204,6 +273,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
         "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// same, 16 columns
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+        "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
