@@ -107,9 +107,16 @@ bool fused_args(const cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperati
   if (!aligned) return false;
   const std::uint64_t m_exp = m * fpe, k_exp = k * fpe;
   if (h->tuning.fused != 1) {
-    // Measured crossover (B200): the on-the-fly split wins while the K loop is short enough
-    // that the split pass and its workspace traffic weigh as much as the products themselves.
-    if (k_exp > 1024) return false;
+    // Measured crossover (B200, FP16TCEC, one call, ms; pre-split path / this kernel):
+    //   512 x complex 256^3      0.51 / 0.43      2048 x real 128^3        0.38 / 0.09
+    //   512 x real 256^3         0.20 / 0.15      64 x real 1024^3         0.53 / 0.87
+    //   real 4096 x 4096 x 512   0.086 / 0.113    real 8192 x 8192 x 256   0.17 / 0.24
+    //   real 1024^3              0.025 / 0.036    real 4096^3              0.37 / 0.81
+    // The on-the-fly split wins for strided batches of small matrices, where the split pass,
+    // its workspace traffic and a second launch weigh as much as the products; a single
+    // matrix, large tiles counts or a long K loop are better off pre-split (every operand
+    // element is converted once per tile that uses it).
+    if (batch < 8 || m_exp > 512 || n > 512 || k_exp > 1024) return false;
   }
   out->a = reinterpret_cast<const float *>(a);
   out->b = reinterpret_cast<const float *>(b);

@@ -45,5 +45,6 @@ bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_
 
 // CTA-pair kernel (tcec_gemm_pair.cu): 256 x 256 tile per cluster of two CTAs.
 cudaError_t launch_tcec_gemm_pair(const TcecGemmArgs &a, cudaStream_t stream);
+cudaError_t launch_tcec_gemm_pair_auto(const TcecGemmArgs &a, cudaStream_t stream);
 
 } // namespace cumpsgemm_b200

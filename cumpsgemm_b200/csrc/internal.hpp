@@ -220,6 +220,9 @@ struct SplitArgs {
 };
 // Splits op(A) and op(B) of one GEMM in a single launch.
 cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream);
+// Same, with the kind taken on the device from dyn->gemm_mode (`kind` of the arguments is
+// ignored; dyn must be set and the panels sized for TF32).
+cudaError_t launch_split_pair_auto(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream);
 
 // ---------------------------------------------------------------- TCEC GEMM
 struct TcecGemmArgs {
@@ -247,6 +250,9 @@ struct TcecGemmArgs {
   Tuning tuning;
 };
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
+// AUTO: one launch that reads dyn->gemm_mode and runs the FP16 or the TF32 pipeline
+// (error-corrected kinds only).  `a` describes the problem; its `kind` is ignored.
+cudaError_t launch_tcec_gemm_auto(const TcecGemmArgs &a, cudaStream_t stream);
 // GEMM that splits its operands on the fly (tcec_gemm_fused.cu): no workspace, FP16 kinds with
 // error correction only.  Sizes are those of the real problem (complex operands expanded:
 // m = 2 * rows of C, k = 2 * K); leading dimensions and strides are in floats.

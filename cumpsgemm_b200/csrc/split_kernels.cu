@@ -367,6 +367,25 @@ __global__ void __launch_bounds__(THREADS, VEC ? 5 : 6) split_dual_kernel(const 
   split_dispatch<KIND, VEC>(j.p, j.path, bid, tile);
 }
 
+// AUTO: the kind (FP16 or TF32 panels) is decided on the device.  Job geometry, source
+// addressing and the workspace are the same for both kinds, so one launch reads the decision
+// and runs the matching bodies (the reference launches the kernels of both kinds and lets the
+// deselected one exit, src/cumpsgemm_kernel.cuh:478-489).
+template <bool VEC>
+__global__ void __launch_bounds__(THREADS, VEC ? 5 : 6)
+    split_dual_auto_kernel(const SplitJob a, const SplitJob b) {
+  __shared__ float tile[TILE][TILE + 1];
+  const uint32_t blocks_a = a.gx * a.gy * a.gz;
+  uint32_t id = blockIdx.x;
+  const SplitJob &j = (id < blocks_a) ? a : b;
+  if (id >= blocks_a) id -= blocks_a;
+  const uint3 bid = make_uint3(id % j.gx, (id / j.gx) % j.gy, id / (j.gx * j.gy));
+  if (j.p.dyn->gemm_mode == CUMPSGEMM_TF32TCEC)
+    split_dispatch<1, VEC>(j.p, j.path, bid, tile);
+  else
+    split_dispatch<0, VEC>(j.p, j.path, bid, tile);
+}
+
 bool make_job(const SplitArgs &a, SplitJob *job) {
   if ((a.rows_pad % TILE) != 0 || (a.k_pad % TILE) != 0) return false;
   SplitParams &p = job->p;
@@ -405,6 +424,20 @@ bool make_job(const SplitArgs &a, SplitJob *job) {
 }
 
 } // namespace
+
+cudaError_t launch_split_pair_auto(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream) {
+  if (a.dyn == nullptr || b.dyn != a.dyn) return cudaErrorInvalidValue;
+  SplitJob ja, jb;
+  if (!make_job(a, &ja) || !make_job(b, &jb)) return cudaErrorInvalidValue;
+  const uint64_t blocks = static_cast<uint64_t>(ja.gx) * ja.gy * ja.gz +
+                          static_cast<uint64_t>(jb.gx) * jb.gy * jb.gz;
+  if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+  const bool vec = (ja.path >= kPathKContig) || (jb.path >= kPathKContig);
+  const unsigned grid = static_cast<unsigned>(blocks);
+  if (vec) split_dual_auto_kernel<true><<<grid, THREADS, 0, stream>>>(ja, jb);
+  else split_dual_auto_kernel<false><<<grid, THREADS, 0, stream>>>(ja, jb);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream) {
   if (a.kind != b.kind) return cudaErrorInvalidValue;

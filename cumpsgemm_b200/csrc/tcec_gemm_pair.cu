@@ -88,9 +88,8 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t tile, const GemmKernelP
 }
 
 template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-    tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                          const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
+__device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
+                                          const GemmKernelParams &p) {
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, 2 * BM_CTA, BN_PAIR);
@@ -411,9 +410,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
-template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
-  auto kernel = tcec_gemm_pair_kernel<KIND>;
-  // per device, once (any thread): shared-memory attribute and the number of co-resident clusters
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
+  pair_body<KIND>(map_a, map_b, p);
+}
+
+// AUTO: both kinds' tensor maps and parameters travel with the launch; the device-side
+// decision picks the pipeline (uniform over the grid).  The reference launches the kernels of
+// both kinds and lets the deselected one exit at once (src/cumpsgemm_kernel.cuh:478-489).
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_pair_auto_kernel(const __grid_constant__ CUtensorMap map_a16,
+                               const __grid_constant__ CUtensorMap map_b16,
+                               const GemmKernelParams p16,
+                               const __grid_constant__ CUtensorMap map_a32,
+                               const __grid_constant__ CUtensorMap map_b32,
+                               const GemmKernelParams p32) {
+  if (p16.dyn->gemm_mode == CUMPSGEMM_TF32TCEC)
+    pair_body<1>(map_a32, map_b32, p32);
+  else
+    pair_body<0>(map_a16, map_b16, p16);
+}
+
+// Per device and kernel, once (any thread): shared-memory attribute and the number of
+// clusters the device can keep resident.  TAG tells the kernels apart (two of them have the
+// same function type, which alone would make them share the statics below).
+template <int TAG, class Kernel> cudaError_t pair_setup(Kernel kernel, int *clusters_out) {
   static std::once_flag once[64];
   static cudaError_t setup_error[64];
   static int max_clusters[64];
@@ -440,21 +463,26 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     }
     max_clusters[dev] = clusters > 0 ? clusters : 1;
   });
-  if (setup_error[dev] != cudaSuccess) return setup_error[dev];
+  *clusters_out = max_clusters[dev];
+  return setup_error[dev];
+}
+
+// Tensor maps and kernel parameters of one kind.  Returns false on invalid sizes.
+bool pair_prepare(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, CUtensorMap *map_b,
+                  GemmKernelParams *pp) {
   const uint32_t planes = a.batch * 2u;
-  CUtensorMap map_a, map_b;
-  if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, 128) ||
-      !make_panel_map(&map_b, a.kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, 128)) {
-    return cudaErrorInvalidValue;
+  if (!make_panel_map(map_a, kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, 128) ||
+      !make_panel_map(map_b, kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, 128)) {
+    return false;
   }
-  GemmKernelParams p;
+  GemmKernelParams &p = *pp;
   p.c = a.c;
   p.c_array = a.c_array;
   p.ldc = a.ldc;
   p.stride_c = a.stride_c;
   p.m = a.m;
   p.n = a.n;
-  const uint32_t es = (a.kind == SplitKind::fp16) ? 2u : 4u;
+  const uint32_t es = (kind == SplitKind::fp16) ? 2u : 4u;
   p.k_blocks = a.k_pad / (ROW_BYTES / es);
   p.tiles_m = (a.m + 2 * BM_CTA - 1) / (2 * BM_CTA);
   p.tiles_n = (a.n + BN_PAIR - 1) / BN_PAIR;
@@ -462,7 +490,7 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   p.alpha_i = a.alpha_i;
   p.beta_r = a.beta_r;
   p.beta_i = a.beta_i;
-  p.lo_scale_inv = (a.kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
+  p.lo_scale_inv = (kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
   p.is_complex = a.is_complex ? 1 : 0;
   p.dyn = a.dyn;
   p.status = a.dev_status;
@@ -487,28 +515,45 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
     const uint32_t k_per_stage = ROW_BYTES / es;
     const uint32_t k_total = p.k_blocks * k_per_stage;
     uint32_t first_k = (k_total >= 8192u) ? 512u : (k_total >= 2048u ? 256u : 128u);
-    if (a.kind != SplitKind::fp16) first_k /= 2u;
+    if (kind != SplitKind::fp16) first_k /= 2u;
     const int fv = a.tuning.first_chunk;
     p.first_chunk = (fv >= 1) ? static_cast<uint32_t>(fv) : first_k / k_per_stage;
     if (p.first_chunk < p.drain_chunk) p.first_chunk = p.drain_chunk;
   }
   const uint64_t total = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
-  if (total == 0 || total > 0x7fffffffull) return cudaErrorInvalidValue;
-  if (a.rows_pad_a < p.tiles_m * 2 * BM_CTA || a.rows_pad_b < p.tiles_n * BN_PAIR)
-    return cudaErrorInvalidValue;
+  if (total == 0 || total > 0x7fffffffull) return false;
+  if (a.rows_pad_a < p.tiles_m * 2 * BM_CTA || a.rows_pad_b < p.tiles_n * BN_PAIR) return false;
   p.total_tiles = static_cast<uint32_t>(total);
-  const uint32_t clusters = static_cast<uint32_t>(
-      total < static_cast<uint64_t>(max_clusters[dev]) ? total : max_clusters[dev]);
   p.wave_counter = nullptr;
-  // Pacing pays when tiles are long (the drift it removes is 2 % of a tile) and clusters share
-  // panel rows; for short tiles a barrier per tile costs more than it saves.
-  if (a.wave_counter != nullptr && total > clusters && p.k_blocks >= kPaceMinStages) {
-    if (a.tuning.pace != 0) {
-      const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
-      if (me != cudaSuccess) return me;
-      p.wave_counter = a.wave_counter;
-    }
+  return true;
+}
+
+// Pacing pays when tiles are long (the drift it removes is 2 % of a tile) and clusters share
+// panel rows; for short tiles a barrier per tile costs more than it saves.
+cudaError_t pair_pacing(const TcecGemmArgs &a, uint32_t clusters, GemmKernelParams *p,
+                        cudaStream_t stream) {
+  if (a.wave_counter != nullptr && p->total_tiles > clusters && p->k_blocks >= kPaceMinStages &&
+      a.tuning.pace != 0) {
+    const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
+    if (me != cudaSuccess) return me;
+    p->wave_counter = a.wave_counter;
   }
+  return cudaSuccess;
+}
+
+template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
+  auto kernel = tcec_gemm_pair_kernel<KIND>;
+  int max_clusters = 1;
+  const cudaError_t se = pair_setup<KIND>(kernel, &max_clusters);
+  if (se != cudaSuccess) return se;
+  CUtensorMap map_a, map_b;
+  GemmKernelParams p;
+  if (!pair_prepare(a, KIND == 0 ? SplitKind::fp16 : SplitKind::tf32, &map_a, &map_b, &p))
+    return cudaErrorInvalidValue;
+  const uint32_t clusters =
+      p.total_tiles < static_cast<uint32_t>(max_clusters) ? p.total_tiles : max_clusters;
+  const cudaError_t pe = pair_pacing(a, clusters, &p, stream);
+  if (pe != cudaSuccess) return pe;
   kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError();
 }
@@ -518,6 +563,28 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
 cudaError_t launch_tcec_gemm_pair(const TcecGemmArgs &a, cudaStream_t stream) {
   if (!a.error_correction) return cudaErrorInvalidValue;
   return (a.kind == SplitKind::fp16) ? launch_pair<0>(a, stream) : launch_pair<1>(a, stream);
+}
+
+cudaError_t launch_tcec_gemm_pair_auto(const TcecGemmArgs &a, cudaStream_t stream) {
+  if (!a.error_correction || a.dyn == nullptr) return cudaErrorInvalidValue;
+  auto kernel = tcec_gemm_pair_auto_kernel;
+  int max_clusters = 1;
+  const cudaError_t se = pair_setup<2>(kernel, &max_clusters);
+  if (se != cudaSuccess) return se;
+  CUtensorMap a16, b16, a32, b32;
+  GemmKernelParams p16, p32;
+  if (!pair_prepare(a, SplitKind::fp16, &a16, &b16, &p16) ||
+      !pair_prepare(a, SplitKind::tf32, &a32, &b32, &p32))
+    return cudaErrorInvalidValue;
+  const uint32_t clusters =
+      p16.total_tiles < static_cast<uint32_t>(max_clusters) ? p16.total_tiles : max_clusters;
+  // pacing depends on the K loop length, which differs by kind: one counter serves whichever runs
+  cudaError_t pe = pair_pacing(a, clusters, &p16, stream);
+  if (pe == cudaSuccess && p16.wave_counter == nullptr) pe = pair_pacing(a, clusters, &p32, stream);
+  else if (pe == cudaSuccess) p32.wave_counter = a.wave_counter;
+  if (pe != cudaSuccess) return pe;
+  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(a16, b16, p16, a32, b32, p32);
+  return cudaGetLastError();
 }
 
 } // namespace cumpsgemm_b200
