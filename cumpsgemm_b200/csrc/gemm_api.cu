@@ -272,80 +272,84 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   cudaError_t err = cudaSuccess;
   for (std::uint64_t b0 = 0; b0 < batch && err == cudaSuccess; b0 += chunk) {
     const std::uint32_t nb = static_cast<std::uint32_t>(std::min<std::uint64_t>(chunk, batch - b0));
-    for (int kind_i = 0; kind_i < 2 && err == cudaSuccess; ++kind_i) {
-      const SplitKind kind = kind_i == 0 ? SplitKind::fp16 : SplitKind::tf32;
-      if ((kind == SplitKind::fp16 && !want_fp16) || (kind == SplitKind::tf32 && !want_tf32))
-        continue;
-      SplitArgs sa;
-      sa.kind = kind;
-      sa.operand = Operand::A;
-      sa.is_complex = is_complex;
-      sa.conjugate = is_complex && op_A == CUBLAS_OP_C;
-      sa.src_k_contig = !a_n;
-      sa.rows = m;
-      sa.k = k;
-      sa.src = ptr_arrays ? nullptr : a + b0 * stridea;
-      sa.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(a_array + b0) : nullptr;
-      sa.ld = lda;
-      sa.stride = stridea;
-      sa.batch = nb;
-      sa.panel = ws_a;
-      sa.rows_pad = rows_pad_a;
-      sa.k_pad = k_pad;
-      sa.with_lo = ec;
-      sa.dyn = dyn;
-      cuMpSGEMM_handle::TimingTriple tt{};
-      if (h->kernel_timing) {
-        for (auto &e : tt.e) cudaEventCreate(&e);
-        cudaEventRecord(tt.e[0], h->cuda_stream);
-      }
-      SplitArgs sb = sa;
-      sb.operand = Operand::B;
-      sb.conjugate = is_complex && op_B == CUBLAS_OP_C;
-      sb.src_k_contig = b_n;
-      sb.rows = n;
-      sb.src = ptr_arrays ? nullptr : b + b0 * strideb;
-      sb.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(b_array + b0) : nullptr;
-      sb.ld = ldb;
-      sb.stride = strideb;
-      sb.panel = ws_b;
-      sb.rows_pad = rows_pad_b;
-      err = launch_split_pair(sa, sb, h->cuda_stream);
-      if (err != cudaSuccess) break;
-      if (h->kernel_timing) cudaEventRecord(tt.e[1], h->cuda_stream);
+    // AUTO: one split launch and one GEMM launch whose kernels read the device-side decision
+    // and run the FP16 or the TF32 pipeline; every other mode: the one kind it names.
+    const bool auto_kind = want_fp16 && want_tf32;
+    const SplitKind kind = want_fp16 ? SplitKind::fp16 : SplitKind::tf32;
+    SplitArgs sa;
+    sa.kind = kind;
+    sa.operand = Operand::A;
+    sa.is_complex = is_complex;
+    sa.conjugate = is_complex && op_A == CUBLAS_OP_C;
+    sa.src_k_contig = !a_n;
+    sa.rows = m;
+    sa.k = k;
+    sa.src = ptr_arrays ? nullptr : a + b0 * stridea;
+    sa.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(a_array + b0) : nullptr;
+    sa.ld = lda;
+    sa.stride = stridea;
+    sa.batch = nb;
+    sa.panel = ws_a;
+    sa.rows_pad = rows_pad_a;
+    sa.k_pad = k_pad;
+    sa.with_lo = ec;
+    sa.dyn = dyn;
+    cuMpSGEMM_handle::TimingTriple tt{};
+    if (h->kernel_timing) {
+      for (auto &e : tt.e) cudaEventCreate(&e);
+      cudaEventRecord(tt.e[0], h->cuda_stream);
+    }
+    SplitArgs sb = sa;
+    sb.operand = Operand::B;
+    sb.conjugate = is_complex && op_B == CUBLAS_OP_C;
+    sb.src_k_contig = b_n;
+    sb.rows = n;
+    sb.src = ptr_arrays ? nullptr : b + b0 * strideb;
+    sb.src_array = ptr_arrays ? reinterpret_cast<const void *const *>(b_array + b0) : nullptr;
+    sb.ld = ldb;
+    sb.stride = strideb;
+    sb.panel = ws_b;
+    sb.rows_pad = rows_pad_b;
+    err = auto_kind ? launch_split_pair_auto(sa, sb, h->cuda_stream)
+                    : launch_split_pair(sa, sb, h->cuda_stream);
+    if (err != cudaSuccess) break;
+    if (h->kernel_timing) cudaEventRecord(tt.e[1], h->cuda_stream);
 
-      TcecGemmArgs g;
-      g.kind = kind;
-      g.error_correction = ec;
-      g.m = static_cast<std::uint32_t>(m_exp);
-      g.n = static_cast<std::uint32_t>(n);
-      g.k_pad = k_pad;
-      g.rows_pad_a = rows_pad_a;
-      g.rows_pad_b = rows_pad_b;
-      g.batch = nb;
-      g.panel_a = ws_a;
-      g.panel_b = ws_b;
-      g.c = ptr_arrays ? nullptr : reinterpret_cast<float *>(c + b0 * stridec);
-      g.c_array = ptr_arrays ? reinterpret_cast<float *const *>(c_array + b0) : nullptr;
-      g.ldc = ldc * fpe;
-      g.stride_c = stridec * fpe;
-      g.alpha_r = Scalar<T>::re(alpha);
-      g.alpha_i = Scalar<T>::im(alpha);
-      g.beta_r = Scalar<T>::re(beta);
-      g.beta_i = Scalar<T>::im(beta);
-      g.is_complex = is_complex;
-      g.dyn = dyn;
-      g.tile_n = tile_n;
-      g.dev_status = h->dev_status;
-      g.wave_counter = reinterpret_cast<unsigned int *>(h->dev_status + 1);
-      g.debug = h->debug_buffer;
-      g.tuning = h->tuning;
+    TcecGemmArgs g;
+    g.kind = kind;
+    g.error_correction = ec;
+    g.m = static_cast<std::uint32_t>(m_exp);
+    g.n = static_cast<std::uint32_t>(n);
+    g.k_pad = k_pad;
+    g.rows_pad_a = rows_pad_a;
+    g.rows_pad_b = rows_pad_b;
+    g.batch = nb;
+    g.panel_a = ws_a;
+    g.panel_b = ws_b;
+    g.c = ptr_arrays ? nullptr : reinterpret_cast<float *>(c + b0 * stridec);
+    g.c_array = ptr_arrays ? reinterpret_cast<float *const *>(c_array + b0) : nullptr;
+    g.ldc = ldc * fpe;
+    g.stride_c = stridec * fpe;
+    g.alpha_r = Scalar<T>::re(alpha);
+    g.alpha_i = Scalar<T>::im(alpha);
+    g.beta_r = Scalar<T>::re(beta);
+    g.beta_i = Scalar<T>::im(beta);
+    g.is_complex = is_complex;
+    g.dyn = dyn;
+    g.tile_n = tile_n;
+    g.dev_status = h->dev_status;
+    g.wave_counter = reinterpret_cast<unsigned int *>(h->dev_status + 1);
+    g.debug = h->debug_buffer;
+    g.tuning = h->tuning;
+    if (auto_kind)
+      err = use_pair ? launch_tcec_gemm_pair_auto(g, h->cuda_stream)
+                     : launch_tcec_gemm_auto(g, h->cuda_stream);
+    else
       err = use_pair ? launch_tcec_gemm_pair(g, h->cuda_stream)
                      : launch_tcec_gemm(g, h->cuda_stream);
-      if (h->kernel_timing) {
-        cudaEventRecord(tt.e[2], h->cuda_stream);
-        h->timing_events.push_back(tt);
-      }
+    if (h->kernel_timing) {
+      cudaEventRecord(tt.e[2], h->cuda_stream);
+      h->timing_events.push_back(tt);
     }
   }
   if (prof) h->exp_stats.profiler.stop("gemm_kernel", h->cuda_stream);

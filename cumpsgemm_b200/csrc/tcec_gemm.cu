@@ -57,9 +57,8 @@ template <int KIND> __device__ __forceinline__ void mma_ss(uint32_t d, uint64_t 
 }
 
 template <int KIND, int BN, bool EC>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-    tcec_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
-                     const __grid_constant__ CUtensorMap map_b, const KernelParams p) {
+__device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
+                                               const KernelParams &p) {
   using Cfg = TileCfg<BN, EC>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
@@ -319,6 +318,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   }
 }
 
+template <int KIND, int BN, bool EC>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b, const KernelParams p) {
+  tcec_gemm_body<KIND, BN, EC>(map_a, map_b, p);
+}
+
+// AUTO: the kind is decided on the device; both kinds' tensor maps and parameters travel with
+// the launch (see tcec_gemm_pair.cu).  Shared memory is sized for the TF32 kind's stages,
+// which are the same bytes as the FP16 kind's.
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    tcec_gemm_auto_kernel(const __grid_constant__ CUtensorMap map_a16,
+                          const __grid_constant__ CUtensorMap map_b16, const KernelParams p16,
+                          const __grid_constant__ CUtensorMap map_a32,
+                          const __grid_constant__ CUtensorMap map_b32, const KernelParams p32) {
+  if (p16.dyn->gemm_mode == CUMPSGEMM_TF32TCEC)
+    tcec_gemm_body<1, BN, true>(map_a32, map_b32, p32);
+  else
+    tcec_gemm_body<0, BN, true>(map_a16, map_b16, p16);
+}
+
 } // namespace
 
 // ---------------------------------------------------------------- host side
@@ -366,34 +387,23 @@ bool make_panel_map(CUtensorMap *map, SplitKind kind, const void *panel, uint32_
 
 namespace {
 
-template <int KIND, int BN, bool EC>
-cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
-  using Cfg = TileCfg<BN, EC>;
-  auto kernel = tcec_gemm_kernel<KIND, BN, EC>;
-  static std::once_flag once[64];
-  static cudaError_t setup_error[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  std::call_once(once[dev], [&]() {
-    setup_error[dev] = cudaFuncSetAttribute(
-        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-  });
-  if (setup_error[dev] != cudaSuccess) return setup_error[dev];
+// Tensor maps, kernel parameters and grid size of one kind.
+template <int BN, bool EC>
+bool prepare_variant(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, CUtensorMap *map_b,
+                     KernelParams *pp, unsigned *grid_out) {
   const uint32_t planes = a.batch * (EC ? 2u : 1u);
-  CUtensorMap map_a, map_b;
-  if (!make_panel_map(&map_a, a.kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, BM) ||
-      !make_panel_map(&map_b, a.kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, BN)) {
-    return cudaErrorInvalidValue;
+  if (!make_panel_map(map_a, kind, a.panel_a, a.k_pad, a.rows_pad_a, planes, BM) ||
+      !make_panel_map(map_b, kind, a.panel_b, a.k_pad, a.rows_pad_b, planes, BN)) {
+    return false;
   }
-  KernelParams p;
+  KernelParams &p = *pp;
   p.c = a.c;
   p.c_array = a.c_array;
   p.ldc = a.ldc;
   p.stride_c = a.stride_c;
   p.m = a.m;
   p.n = a.n;
-  const uint32_t es = (a.kind == SplitKind::fp16) ? 2u : 4u;
+  const uint32_t es = (kind == SplitKind::fp16) ? 2u : 4u;
   p.k_blocks = a.k_pad / (ROW_BYTES / es);
   p.tiles_m = (a.m + BM - 1) / BM;
   p.tiles_n = (a.n + BN - 1) / BN;
@@ -401,7 +411,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   p.alpha_i = a.alpha_i;
   p.beta_r = a.beta_r;
   p.beta_i = a.beta_i;
-  p.lo_scale_inv = (a.kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
+  p.lo_scale_inv = (kind == SplitKind::fp16) ? (1.f / 2048.f) : 1.f;
   p.is_complex = a.is_complex ? 1 : 0;
   p.dyn = a.dyn;
   p.status = a.dev_status;
@@ -411,8 +421,54 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   p.first_chunk = 1;
   p.total_tiles = 0;
   const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
-  if (grid == 0 || grid > 0x7fffffffull) return cudaErrorInvalidValue;
-  kernel<<<static_cast<unsigned>(grid), NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  if (grid == 0 || grid > 0x7fffffffull) return false;
+  *grid_out = static_cast<unsigned>(grid);
+  return true;
+}
+
+// Shared-memory attribute of a kernel, once per device.  TAG tells kernels of equal function
+// type apart.
+template <int TAG, class Kernel> cudaError_t smem_setup(Kernel kernel, int smem_bytes) {
+  static std::once_flag once[64];
+  static cudaError_t setup_error[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [&]() {
+    setup_error[dev] =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  });
+  return setup_error[dev];
+}
+
+template <int KIND, int BN, bool EC>
+cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
+  using Cfg = TileCfg<BN, EC>;
+  auto kernel = tcec_gemm_kernel<KIND, BN, EC>;
+  const cudaError_t se = smem_setup<KIND * 8 + (BN / 64) * 2 + (EC ? 1 : 0)>(kernel, Cfg::SMEM_BYTES);
+  if (se != cudaSuccess) return se;
+  CUtensorMap map_a, map_b;
+  KernelParams p;
+  unsigned grid = 0;
+  if (!prepare_variant<BN, EC>(a, KIND == 0 ? SplitKind::fp16 : SplitKind::tf32, &map_a, &map_b, &p,
+                               &grid))
+    return cudaErrorInvalidValue;
+  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return cudaGetLastError();
+}
+
+template <int BN> cudaError_t launch_auto_variant(const TcecGemmArgs &a, cudaStream_t stream) {
+  using Cfg = TileCfg<BN, true>;
+  auto kernel = tcec_gemm_auto_kernel<BN>;
+  const cudaError_t se = smem_setup<100 + BN / 64>(kernel, Cfg::SMEM_BYTES);
+  if (se != cudaSuccess) return se;
+  CUtensorMap a16, b16, a32, b32;
+  KernelParams p16, p32;
+  unsigned grid = 0;
+  if (!prepare_variant<BN, true>(a, SplitKind::fp16, &a16, &b16, &p16, &grid) ||
+      !prepare_variant<BN, true>(a, SplitKind::tf32, &a32, &b32, &p32, &grid))
+    return cudaErrorInvalidValue;
+  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(a16, b16, p16, a32, b32, p32);
   return cudaGetLastError();
 }
 
@@ -458,6 +514,20 @@ cudaError_t launch_bounded_wait_selftest(int *dev_status, unsigned long long lim
                                          unsigned long long *dev_waited_ns, cudaStream_t stream) {
   bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(dev_status, limit_ns, dev_waited_ns);
   return cudaGetLastError();
+}
+
+cudaError_t launch_tcec_gemm_auto(const TcecGemmArgs &a, cudaStream_t stream) {
+  if (!a.error_correction || a.dyn == nullptr) return cudaErrorInvalidValue;
+  switch (a.tile_n) {
+  case 256:
+    return launch_auto_variant<256>(a, stream);
+  case 128:
+    return launch_auto_variant<128>(a, stream);
+  case 64:
+    return launch_auto_variant<64>(a, stream);
+  default:
+    return cudaErrorInvalidValue;
+  }
 }
 
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream) {
