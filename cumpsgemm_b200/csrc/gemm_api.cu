@@ -241,11 +241,34 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
     return CUBLAS_STATUS_SUCCESS;
   }
 
-  const TileChoice choice = pick_tile(h->tuning, h->num_sms, m_exp, n, batch, ec);
+  TileChoice choice = pick_tile(h->tuning, h->num_sms, m_exp, n, batch, ec);
+  // Few tiles and a long K loop (the shapes the reference hands to its atomic split-K kernel,
+  // src/cumpsgemm.cu:272-304): cut K into slices, one CTA each, so that the tiles fill the
+  // GPU; the slices' partial sums are added in a fixed order by a second kernel.  The widest
+  // tile the problem fills is taken (fewest operand bytes per product), and each slice keeps
+  // at least 256 k values.
+  std::uint32_t k_slices = 1;
+  {
+    const std::uint32_t k_pad64 = static_cast<std::uint32_t>(round_up(k_exp, 64));
+    int wide = (n > 128) ? 256 : (n > 64 ? 128 : 64);
+    if (h->tuning.tile_n != 0) wide = h->tuning.tile_n;
+    const std::uint64_t tiles = ((m_exp + 127) / 128) * ((n + wide - 1) / wide) * batch;
+    const bool forced = h->tuning.split_k > 1;
+    if (!ptr_arrays && h->tuning.split_k != 0 && h->tuning.pair != 1 &&
+        (forced || (k_pad64 >= 2048 && 2 * tiles <= h->num_sms))) {
+      std::uint32_t wanted = static_cast<std::uint32_t>(h->num_sms / tiles);
+      wanted = std::min<std::uint32_t>(wanted, k_pad64 / 256);
+      if (forced) wanted = static_cast<std::uint32_t>(h->tuning.split_k);
+      k_slices = split_k_slices(k_pad64, wanted);
+      if (k_slices > 1) choice = TileChoice{wide, false};
+    }
+  }
   const int tile_n = choice.tile_n;
   const bool use_pair = choice.pair;
+  // tile class, or 100 for the split-K path as in the reference (src/cumpsgemm.cu:283-285)
   if (used_kernel_module_id != nullptr)
-    *used_kernel_module_id = (tile_n == 256) ? 0u : (tile_n == 128 ? 1u : 2u);
+    *used_kernel_module_id =
+        (k_slices > 1) ? 100u : (tile_n == 256) ? 0u : (tile_n == 128 ? 1u : 2u);
 
   const std::uint32_t rows_pad_a =
       static_cast<std::uint32_t>(round_up(m_exp, use_pair ? 256 : 128));
@@ -257,15 +280,19 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   const std::size_t bytes_b_1 = planes * rows_pad_b * static_cast<std::size_t>(k_pad) * es_max;
   const std::size_t limit =
       h->workspace_limit_bytes ? h->workspace_limit_bytes : kDefaultWorkspaceLimit;
-  std::uint64_t chunk = std::max<std::uint64_t>(1, limit / (bytes_a_1 + bytes_b_1));
+  // split-K partial sums: k_slices blocks of m x n floats per batch entry, behind the panels
+  const std::size_t bytes_p_1 =
+      (k_slices > 1) ? static_cast<std::size_t>(k_slices) * m_exp * n * sizeof(float) : 0;
+  std::uint64_t chunk = std::max<std::uint64_t>(1, limit / (bytes_a_1 + bytes_b_1 + bytes_p_1));
   chunk = std::min<std::uint64_t>(chunk, batch);
   chunk = std::min<std::uint64_t>(chunk, 32768); // planes of a tensor map, tiles of a launch
-  if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1))) {
+  if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1 + bytes_p_1))) {
     log_error("failed to allocate the operand workspace");
     return CUBLAS_STATUS_ALLOC_FAILED;
   }
   char *ws_a = reinterpret_cast<char *>(h->workspace);
   char *ws_b = ws_a + chunk * bytes_a_1;
+  float *ws_p = reinterpret_cast<float *>(ws_b + chunk * bytes_b_1);
 
   const bool prof = h->exp_stats.profiling_enabled;
   if (prof) h->exp_stats.profiler.start("gemm_kernel", h->cuda_stream);
@@ -341,12 +368,15 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
     g.wave_counter = reinterpret_cast<unsigned int *>(h->dev_status + 1);
     g.debug = h->debug_buffer;
     g.tuning = h->tuning;
+    g.k_slices = k_slices;
+    g.partial = (k_slices > 1) ? ws_p : nullptr;
     if (auto_kind)
       err = use_pair ? launch_tcec_gemm_pair_auto(g, h->cuda_stream)
                      : launch_tcec_gemm_auto(g, h->cuda_stream);
     else
       err = use_pair ? launch_tcec_gemm_pair(g, h->cuda_stream)
                      : launch_tcec_gemm(g, h->cuda_stream);
+    if (err == cudaSuccess && k_slices > 1) err = launch_splitk_reduce(g, h->cuda_stream);
     if (h->kernel_timing) {
       cudaEventRecord(tt.e[2], h->cuda_stream);
       h->timing_events.push_back(tt);

@@ -35,6 +35,13 @@ struct GemmKernelParams {
   // Pair tiles in the whole launch (tiles_m * tiles_n * batch); the persistent pair kernel
   // walks them with a stride of the number of clusters in the grid.
   uint32_t total_tiles;
+  // Split-K (single-CTA kernel): the K loop of a tile is cut into k_slices pieces of
+  // slice_blocks stages, one CTA each (blockIdx.x = tile * k_slices + slice).  With more than
+  // one slice a CTA writes its plain partial sum (alpha = 1, beta = 0, no complex arithmetic)
+  // to c + slice * slice_stride floats, and a second kernel adds the slices in a fixed order.
+  uint32_t k_slices;
+  uint32_t slice_blocks;
+  uint64_t slice_stride;
 };
 
 // Tensor map over a K-blocked panel: dims {elements per 128 bytes, rows_pad, planes * k_blocks},

@@ -43,6 +43,8 @@ Tuning read_tuning_env() {
   t.pace = as_int("CUMPSGEMM_PACE", 1) != 0 ? 1 : 0;
   const int fu = as_int("CUMPSGEMM_FUSED", -1);
   t.fused = (fu == 0 || fu == 1) ? fu : -1;
+  const int sk = as_int("CUMPSGEMM_SPLIT_K", -1);
+  t.split_k = (sk >= 0) ? sk : -1;
   return t;
 }
 void log_warning(const std::string &s) {

@@ -72,7 +72,8 @@ struct Profiler {
 // CTA-pair kernel off / on, CUMPSGEMM_DRAIN_CHUNK and CUMPSGEMM_FIRST_CHUNK the number of
 // K stages per accumulator drain (pair kernel), CUMPSGEMM_PACE = 0 the wave pacing off,
 // CUMPSGEMM_FUSED = 0 / 1 the kernel that splits operands on the fly off / on wherever it is
-// applicable.
+// applicable, CUMPSGEMM_SPLIT_K = 0 / n the K-slicing of problems with few tiles off / to n
+// slices.
 struct Tuning {
   int tile_n = 0;      // 0 = by rule
   int pair = -1;       // -1 = by rule
@@ -80,6 +81,7 @@ struct Tuning {
   int first_chunk = 0; // 0 = default
   int pace = 1;
   int fused = -1;      // -1 = by rule
+  int split_k = -1;    // CUMPSGEMM_SPLIT_K: 0 = never, -1 = by rule, n > 1 = that many slices
 };
 Tuning read_tuning_env();
 
@@ -248,7 +250,19 @@ struct TcecGemmArgs {
   // (zeroed by the launcher before every launch); null switches the pacing off.
   unsigned int *wave_counter = nullptr;
   Tuning tuning;
+  // Split-K (single-CTA kernel only): k_slices > 1 cuts the K loop into that many CTAs per tile,
+  // which write plain partial sums to `partial` (k_slices * batch * m * n floats); the caller
+  // then runs launch_splitk_reduce.  split_k_slices() gives the slice count that makes every
+  // slice the same whole number of 64-k-value units (0 or 1: no split).
+  std::uint32_t k_slices = 1;
+  float *partial = nullptr;
 };
+// Slices actually used when `wanted` are asked for a K loop of k_pad values.
+std::uint32_t split_k_slices(std::uint32_t k_pad, std::uint32_t wanted);
+// C = alpha * unscale * sum_s partial[s] + beta * C with the slices added in ascending order
+// (run-to-run bit-identical, unlike the reference's atomic accumulation,
+// src/cumpsgemm.cu:272-304 and src/dmem_accessor.hpp:352-395).  Sizes as in TcecGemmArgs.
+cudaError_t launch_splitk_reduce(const TcecGemmArgs &a, cudaStream_t stream);
 cudaError_t launch_tcec_gemm(const TcecGemmArgs &a, cudaStream_t stream);
 // AUTO: one launch that reads dyn->gemm_mode and runs the FP16 or the TF32 pipeline
 // (error-corrected kinds only).  `a` describes the problem; its `kind` is ignored.

@@ -88,8 +88,10 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
   // ---- tile coordinates: grouped raster so that concurrently resident CTAs
   //      share A and B panels in L2
   const uint32_t tiles_per_batch = p.tiles_m * p.tiles_n;
-  const uint32_t batch_id = blockIdx.x / tiles_per_batch;
-  const uint32_t t = blockIdx.x - batch_id * tiles_per_batch;
+  const uint32_t slice = blockIdx.x % p.k_slices;
+  const uint32_t tile_linear = blockIdx.x / p.k_slices;
+  const uint32_t batch_id = tile_linear / tiles_per_batch;
+  const uint32_t t = tile_linear - batch_id * tiles_per_batch;
   constexpr uint32_t GROUP_M = 16;
   const uint32_t tiles_in_group = GROUP_M * p.tiles_n;
   const uint32_t group_id = t / tiles_in_group;
@@ -122,7 +124,9 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
-  const uint32_t k_blocks = p.k_blocks;
+  // this CTA's part of the K loop: stages [kb0, kb0 + k_blocks) of the p.k_blocks in a panel
+  const uint32_t kb0 = slice * p.slice_blocks;
+  const uint32_t k_blocks = min(p.slice_blocks, p.k_blocks - kb0);
   const bool dbg = (p.debug != nullptr);
   unsigned long long dbg_wait = 0, dbg_wait2 = 0;
 
@@ -140,10 +144,10 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
         ptx::mbar_arrive_expect_tx(fb, Cfg::STAGE_BYTES);
         uint8_t *st = smem + s * Cfg::STAGE_BYTES;
         // coordinates: (element in the K block, row, plane * k_blocks + K block)
-        const int zh = static_cast<int>(static_cast<uint32_t>(za) * k_blocks + kb);
+        const int zh = static_cast<int>(static_cast<uint32_t>(za) * p.k_blocks + kb0 + kb);
         ptx::tma_load_3d(ptx::smem_u32(st), &map_a, fb, 0, m0, zh);
         if constexpr (EC) {
-          const int zl = zh + static_cast<int>(k_blocks);
+          const int zl = zh + static_cast<int>(p.k_blocks);
           ptx::tma_load_3d(ptx::smem_u32(st + Cfg::A_TILE), &map_a, fb, 0, m0, zl);
           ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE), &map_b, fb, 0, n0, zh);
           ptx::tma_load_3d(ptx::smem_u32(st + 2 * Cfg::A_TILE + Cfg::B_TILE), &map_b, fb, 0, n0,
@@ -256,14 +260,16 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
     if (ok) {
       // C(row, col) = alpha * acc + beta * C(row, col); lanes hold consecutive rows of a
       // column-major C, so each warp store covers 128 contiguous bytes.
-      const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
+      // (split-K partial sums are stored plain; scaling and alpha / beta belong to the reduction)
+      const float unscale = (p.dyn != nullptr && p.k_slices == 1) ? p.dyn->unscale_c : 1.f;
       const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
       const float br = p.beta_r, bi = p.beta_i;
       const bool read_c = (br != 0.f) || (bi != 0.f);
       const uint32_t row = static_cast<uint32_t>(m0) + quarter * 32u + static_cast<uint32_t>(lane);
       const bool row_ok = row < p.m;
       float *cbase = ((p.c_array != nullptr) ? p.c_array[batch_id]
-                                              : p.c + static_cast<uint64_t>(batch_id) * p.stride_c) +
+                                              : p.c + static_cast<uint64_t>(batch_id) * p.stride_c +
+                                                    static_cast<uint64_t>(slice) * p.slice_stride) +
                      row;
       const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
       // Columns go in groups: all loads of a group are issued before its first store (the
@@ -420,7 +426,29 @@ bool prepare_variant(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, 
   p.drain_chunk = 1;
   p.first_chunk = 1;
   p.total_tiles = 0;
-  const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
+  p.k_slices = 1;
+  p.slice_blocks = p.k_blocks;
+  p.slice_stride = 0;
+  if (a.k_slices > 1) {
+    // partial sums: plain floats into the caller's scratch, one m x n block per slice and batch
+    // entry; the slice length is the same number of 64-k-value units for both kinds
+    const uint32_t units = a.k_pad / 64;
+    const uint32_t per_slice_units = (units + a.k_slices - 1) / a.k_slices;
+    p.slice_blocks = per_slice_units * (64 / (ROW_BYTES / es));
+    p.k_slices = (p.k_blocks + p.slice_blocks - 1) / p.slice_blocks;
+    if (p.k_slices != a.k_slices || a.partial == nullptr || a.c_array != nullptr) return false;
+    p.c = a.partial;
+    p.c_array = nullptr;
+    p.ldc = a.m;
+    p.stride_c = static_cast<uint64_t>(a.m) * a.n;
+    p.slice_stride = p.stride_c * a.batch;
+    p.alpha_r = 1.f;
+    p.alpha_i = 0.f;
+    p.beta_r = 0.f;
+    p.beta_i = 0.f;
+    p.is_complex = 0;
+  }
+  const uint64_t grid = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch * p.k_slices;
   if (grid == 0 || grid > 0x7fffffffull) return false;
   *grid_out = static_cast<unsigned>(grid);
   return true;
@@ -513,6 +541,69 @@ __global__ void bounded_wait_selftest_kernel(int *status, unsigned long long lim
 cudaError_t launch_bounded_wait_selftest(int *dev_status, unsigned long long limit_ns,
                                          unsigned long long *dev_waited_ns, cudaStream_t stream) {
   bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(dev_status, limit_ns, dev_waited_ns);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- split-K reduction
+namespace {
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(const float *partial, uint32_t slices, uint64_t slice_stride,
+                         uint64_t total, uint32_t m, uint32_t n, float *c, uint64_t ldc,
+                         uint64_t stride_c, float alpha_r, float alpha_i, float beta_r,
+                         float beta_i, int is_complex, const DynParams *dyn) {
+  const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint64_t per_batch = static_cast<uint64_t>(m) * n;
+  const uint64_t b = idx / per_batch;
+  const uint64_t r = idx - b * per_batch;
+  const uint32_t col = static_cast<uint32_t>(r / m);
+  const uint32_t row = static_cast<uint32_t>(r - static_cast<uint64_t>(col) * m);
+  // slices in ascending order: the sum does not depend on which CTA finished first
+  float sum = 0.f, sum_o = 0.f;
+  const float *pp = partial + idx;
+  for (uint32_t s = 0; s < slices; ++s) sum += pp[s * slice_stride];
+  const float unscale = (dyn != nullptr) ? dyn->unscale_c : 1.f;
+  const float ar = alpha_r * unscale, ai = alpha_i * unscale;
+  float *cp = c + b * stride_c + static_cast<uint64_t>(col) * ldc + row;
+  const bool read_c = (beta_r != 0.f) || (beta_i != 0.f);
+  float out;
+  if (is_complex) {
+    // rows 2i / 2i+1 hold the real / imaginary part of complex row i
+    const float *po = partial + (idx ^ 1ull);
+    for (uint32_t s = 0; s < slices; ++s) sum_o += po[s * slice_stride];
+    const float sgn = (row & 1u) ? 1.f : -1.f;
+    out = ar * sum + sgn * ai * sum_o;
+    if (read_c) {
+      float *co = (row & 1u) ? cp - 1 : cp + 1;
+      out += beta_r * (*cp) + sgn * beta_i * (*co);
+    }
+  } else {
+    out = ar * sum;
+    if (read_c) out = fmaf(beta_r, *cp, out);
+  }
+  // complex: the partner thread reads this element of C as well; all reads happen before the
+  // writes of the pair because both threads are in the same warp (m is even, idx ^ 1 adjacent)
+  __syncwarp();
+  *cp = out;
+}
+} // namespace
+
+std::uint32_t split_k_slices(std::uint32_t k_pad, std::uint32_t wanted) {
+  const std::uint32_t units = k_pad / 64;
+  if (wanted <= 1 || units <= 1) return 1;
+  if (wanted > units) wanted = units;
+  const std::uint32_t per = (units + wanted - 1) / wanted;
+  return (units + per - 1) / per;
+}
+
+cudaError_t launch_splitk_reduce(const TcecGemmArgs &a, cudaStream_t stream) {
+  if (a.k_slices <= 1 || a.partial == nullptr || a.c == nullptr) return cudaErrorInvalidValue;
+  const uint64_t total = static_cast<uint64_t>(a.m) * a.n * a.batch;
+  const uint64_t blocks = (total + 255) / 256;
+  if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+  splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      a.partial, a.k_slices, total, total, a.m, a.n, a.c, a.ldc, a.stride_c, a.alpha_r, a.alpha_i,
+      a.beta_r, a.beta_i, a.is_complex ? 1 : 0, a.dyn);
   return cudaGetLastError();
 }
 

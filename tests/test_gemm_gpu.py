@@ -503,3 +503,83 @@ def test_bounded_wait_gives_up_cleanly(handle, oracle):
     handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c, m, FP16TCEC)
     truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a.cpu().numpy(), m, b.cpu().numpy(), k, 0.0, None, m)
     assert oracle.residual(truth, c.cpu().numpy(), m) < oracle.error_threshold(True, k)
+
+
+# ---------------------------------------------------------------- split-K
+def _split_k_env(handle, value):
+    if value is None:
+        os.environ.pop("CUMPSGEMM_SPLIT_K", None)
+    else:
+        os.environ["CUMPSGEMM_SPLIT_K"] = str(value)
+    handle.reload_tuning_env()
+
+
+def test_split_k_small_c_long_k(handle, oracle):
+    """Few tiles and a long K loop (the shapes the reference gives to its atomic split-K kernel,
+    src/cumpsgemm.cu:272-304): K is cut into slices over many CTAs and the partial sums are
+    added in a fixed order, so the result is right, reported as module 100, and bit-identical
+    from run to run (the reference's atomics are not)."""
+    torch = _torch()
+    m, n, k = 256, 200, 65536
+    a, b = oracle.gen_uniform(1, m * k), oracle.gen_uniform(2, k * n)
+    c0 = oracle.gen_uniform(3, m * n)
+    da, db = _dev(a), _dev(b)
+    truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c0, m)
+    outs = []
+    try:
+        for mode in (FP16TCEC, TF32TCEC):
+            for rep in range(2):
+                dc = _dev(c0.copy())
+                st, mod = handle.gemm_module(N, N, m, n, k, 1.0, da, m, db, k, 0.5, dc, m, mode)
+                assert st == 0 and mod == 100
+                outs.append(dc)
+            assert torch.equal(outs[-1], outs[-2])
+            assert oracle.residual(truth, outs[-1].cpu().numpy(), m) < oracle.error_threshold(True, k)
+        # no worse than an FP32 GEMM, and the unsplit path agrees
+        c32 = c0.copy()
+        oracle.gemm_f32(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c32, m)
+        assert oracle.residual(truth, outs[0].cpu().numpy(), m) <= 1.5 * oracle.residual(truth, c32, m)
+        _split_k_env(handle, 0)
+        dc = _dev(c0.copy())
+        st, mod = handle.gemm_module(N, N, m, n, k, 1.0, da, m, db, k, 0.5, dc, m, FP16TCEC)
+        assert st == 0 and mod != 100
+        assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    finally:
+        _split_k_env(handle, None)
+
+
+@pytest.mark.parametrize("slices", [2, 3, 7])
+def test_split_k_forced_uneven_slices_complex_and_batches(handle, oracle, slices):
+    """Slice counts that do not divide the K loop, ragged sizes, complex alpha / beta (applied by
+    the reduction kernel on interleaved rows), a strided batch, and FP16TCEC_SCALING (the
+    un-scaling factor belongs to the reduction as well)."""
+    torch = _torch()
+    _split_k_env(handle, slices)
+    try:
+        r = _run_complex(handle, oracle, N, Cj, 70, 90, 333, FP16TCEC, 0.5 - 1.5j, -0.25 + 2j, seed=4,
+                         pad=3)
+        assert r < oracle.error_threshold(True, 333)
+        batch, m, n, k = 3, 129, 65, 700
+        a = oracle.gen_uniform(5, m * k * batch)
+        b = oracle.gen_uniform(6, k * n * batch)
+        c0 = oracle.gen_uniform(7, m * n * batch)
+        for mode in (FP16TCEC, TF32TCEC):
+            dc = _dev(c0.copy())
+            handle.gemm_strided_batch(T, N, m, n, k, 2.0, _dev(a), k, m * k, _dev(b), k, k * n, -1.0,
+                                      dc, m, m * n, batch, mode)
+            res = dc.cpu().numpy()
+            for i in range(batch):
+                truth = oracle.gemm_f64(T, N, m, n, k, 2.0, a[i * m * k:], k, b[i * k * n:], k, -1.0,
+                                        c0[i * m * n:], m)
+                assert oracle.residual(truth, res[i * m * n:(i + 1) * m * n], m) < \
+                    oracle.error_threshold(True, k)
+        tiny_a = (oracle.gen_uniform(8, 200 * 512) * np.float32(2.0 ** -26)).astype(np.float32)
+        tiny_b = (oracle.gen_uniform(9, 512 * 100) * np.float32(2.0 ** -22)).astype(np.float32)
+        dc = torch.zeros(200 * 100, device="cuda")
+        handle.gemm(N, N, 200, 100, 512, 1.0, _dev(tiny_a), 200, _dev(tiny_b), 512, 0.0, dc, 200,
+                    SCALING)
+        truth = oracle.gemm_f64(N, N, 200, 100, 512, 1.0, tiny_a, 200, tiny_b, 512, 0.0, None, 200)
+        assert oracle.residual(truth, dc.cpu().numpy(), 200) < oracle.error_threshold(True, 512)
+        assert handle.kernel_status() == 0
+    finally:
+        _split_k_env(handle, None)
