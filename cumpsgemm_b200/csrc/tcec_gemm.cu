@@ -61,7 +61,6 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
                                                const KernelParams &p) {
   using Cfg = TileCfg<BN, EC>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int ELEM_BYTES = (KIND == 0) ? 2 : 4;
   constexpr int K_STEPS = ROW_BYTES / 32;    // tcgen05.mma consumes 32 bytes of K per instruction
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, BM, BN);
@@ -435,8 +434,10 @@ bool prepare_variant(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, 
     const uint32_t units = a.k_pad / 64;
     const uint32_t per_slice_units = (units + a.k_slices - 1) / a.k_slices;
     p.slice_blocks = per_slice_units * (64 / (ROW_BYTES / es));
-    p.k_slices = (p.k_blocks + p.slice_blocks - 1) / p.slice_blocks;
-    if (p.k_slices != a.k_slices || a.partial == nullptr || a.c_array != nullptr) return false;
+    const uint32_t slices = (p.k_blocks + p.slice_blocks - 1) / p.slice_blocks;
+    p.k_slices = static_cast<uint16_t>(slices);
+    if (slices != a.k_slices || slices > 0xffffu || a.partial == nullptr || a.c_array != nullptr)
+      return false;
     p.c = a.partial;
     p.c_array = nullptr;
     p.ldc = a.m;

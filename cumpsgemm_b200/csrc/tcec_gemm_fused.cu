@@ -6,10 +6,11 @@
 // warps read FP32 / complex64 tiles of op(A) and op(B) straight from global memory, split them
 // in registers (same arithmetic as split_kernels.cu, so both paths feed the tensor core the
 // same bits) and write the FP16 hi / lo tiles into shared memory in the 128-byte-swizzled
-// K-major layout a UMMA shared-memory descriptor reads.  Everything behind that point - the
-// three products per stage, D0 drained every chunk and added in FP32 outside the tensor core,
-// D1 kept in TMEM for the whole K loop, the alpha / beta epilogue - is the protocol of
-// tcec_gemm_pair.cu on one CTA.
+// K-major layout a UMMA shared-memory descriptor reads.  Per stage the tensor core then forms
+// the three products hi*hi, hi*lo and lo*hi; every chunk of stages the accumulators are
+// drained and added to an FP32 running sum with round-to-nearest adds outside the tensor core
+// (hi*hi as it is, the two corrections times 2^-11), and the alpha / beta epilogue is the one
+// of tcec_gemm_pair.cu.
 //
 // It pays where the split pass of the two-kernel path costs as much as the GEMM: short K and
 // many small problems (strided batches of a few hundred rows), where writing the panels to HBM
@@ -29,8 +30,16 @@
 // 512*64 + 128*40 + 256*104 = 64512 = the registers the CTA was launched with, so the inc can
 // always be served.
 // Barriers: full[s] (16 arrivals: one per converter warp, after fence.proxy.async), empty[s]
-// (tcgen05.commit), d0_full / d0_empty / d1_full / d1_empty as in the pair kernel.  Every wait
-// is bounded.  No TMA is used at all.
+// (tcgen05.commit), d0_full[b] / d0_empty[b] for the two accumulator buffers that alternate
+// per drain chunk (the epilogue warps drain one while the tensor core fills the other).  Every
+// wait is bounded.  No TMA is used at all.
+//
+// What bounds it (measured with in-kernel time stamps, 128 x 128 tiles): the issuing thread
+// needs about 120 cycles per tcgen05.mma whatever its size (1,000 cycles per stage for eight
+// instructions against 770 cycles of tensor-core work), and a converter warp needs about
+// 2,400 cycles per stage (its loads share the L1 / shared-memory data path with its stores),
+// so a stage takes about 3,000 cycles: a quarter of the tensor-core rate, which is why the
+// dispatch uses this kernel only where the two-kernel path is bound by its HBM round trip.
 //
 // Operand layouts the converters understand (anything else takes the pre-split path):
 //   kcontig  element (r, kk) of the real operand at src[r * ld + kk]      (A with op T, B with
@@ -87,17 +96,19 @@ struct FusedParams {
   // 13 % faster with them than without (0.44 against 0.50 ms for 512 complex 256^3 products),
   // so they stay.
   int diag;
-  GemmKernelParams g;
 };
+// Every kernel parameter stays at or under 128 bytes: a larger struct is read through a pointer
+// (see GemmKernelParams), which is why the operands and the output side travel separately.
+static_assert(sizeof(FusedParams) <= 128, "kernel parameter structs stay within 128 bytes");
 
 template <int BN> struct FusedCfg {
   static constexpr int A_TILE = BM * ROW_BYTES;
   static constexpr int B_TILE = BN * ROW_BYTES;
   static constexpr int STAGE_BYTES = 2 * (A_TILE + B_TILE);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-  // two D0 buffers (alternating per drain chunk) and two D1 buffers (alternating per tile)
+  // two accumulator buffers, alternating per drain chunk, of 2 * BN columns each:
+  // [hi*hi | hi*lo + lo*hi]
   static constexpr uint32_t TMEM_COLS = 4u * BN;
-  static constexpr uint32_t D1_COL = 2u * BN;
 };
 
 // Byte offset of (row r, 16-byte chunk c) inside a K-major tile with 128-byte rows and the
@@ -472,12 +483,12 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t tile, const GemmKernelP
 }
 
 template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const FusedParams fp) {
+__global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const FusedParams fp,
+                                                                         const GemmKernelParams p) {
   using Cfg = FusedCfg<BN>;
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr uint32_t IDESC = ptx::make_idesc(0, BM, BN);
   constexpr int CPT = BN / 2;
-  const GemmKernelParams &p = fp.g;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
@@ -487,9 +498,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
   uint64_t *empty_bar = bars + STAGES;
   uint64_t *d0_full = bars + 2 * STAGES;      // [2]
   uint64_t *d0_empty = bars + 2 * STAGES + 2; // [2]
-  uint64_t *d1_full = bars + 2 * STAGES + 4;  // [2]
-  uint64_t *d1_empty = bars + 2 * STAGES + 6; // [2]
-  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 8);
+  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -504,8 +513,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(ptx::smem_u32(&d0_full[b]), 1);
       ptx::mbar_init(ptx::smem_u32(&d0_empty[b]), NUM_EPI_WARPS);
-      ptx::mbar_init(ptx::smem_u32(&d1_full[b]), 1);
-      ptx::mbar_init(ptx::smem_u32(&d1_empty[b]), NUM_EPI_WARPS);
     }
     *abort_flag = 0;
     ptx::mbar_init_fence();
@@ -532,17 +539,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
       // cycles per stage its own instruction count is on the critical path: stage index,
       // phase bits and chunk boundaries are kept as running counters (no division), and the
       // four operand descriptors of a stage are one base plus a per-stage constant.
-      // chunk_idx counts drain chunks, tile_iter tiles, over the whole launch: chunk c
-      // accumulates in D0 buffer c & 1, tile t keeps its corrections in D1 buffer t & 1, so
-      // the epilogue warps drain one buffer while the tensor core fills the other.
+      // chunk_idx counts drain chunks over the whole launch: chunk c accumulates in buffer
+      // c & 1, so the epilogue warps drain one buffer while the tensor core fills the other.
       const uint64_t desc0 = ptx::make_kmajor_desc<ROW_BYTES>(ptx::smem_u32(smem));
       constexpr uint64_t kStageDesc = Cfg::STAGE_BYTES >> 4;
-      constexpr uint64_t kALo = Cfg::A_TILE >> 4, kBHi = (2 * Cfg::A_TILE) >> 4,
-                         kBLo = (2 * Cfg::A_TILE + Cfg::B_TILE) >> 4;
-      uint32_t s = 0, ph = 0, chunk_idx = 0, tile_iter = 0;
-      for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
-        const uint32_t b1 = tile_iter & 1u;
-        const uint32_t d1 = tmem_base + Cfg::D1_COL + b1 * BN;
+      constexpr uint64_t kALo = Cfg::A_TILE >> 4, kBHi = (2 * Cfg::A_TILE) >> 4;
+      constexpr uint32_t IDESC2 = ptx::make_idesc(0, BM, 2 * BN);
+      uint32_t s = 0, ph = 0, chunk_idx = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         uint32_t chunk_end = 0; // first stage after the current chunk
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
           const bool first_in_chunk = (kb == chunk_end);
@@ -552,7 +556,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
           }
           const bool last_in_chunk = (kb + 1 == chunk_end);
           const uint32_t b0 = chunk_idx & 1u;
-          const uint32_t d0 = tmem_base + b0 * BN;
+          const uint32_t acc_hh = tmem_base + b0 * (2 * BN); // [hi*hi | corrections]
           ok = ptx::mbar_wait_poll(ptx::smem_u32(&full_bar[s]), ph, abort_flag, p.status,
                                    ptx::kErrWaitFull);
           if (!ok) break;
@@ -564,25 +568,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
           }
           ptx::tc_fence_after();
           const uint64_t a_hi = desc0 + s * kStageDesc;
-          const uint64_t a_lo = a_hi + kALo, b_hi = a_hi + kBHi, b_lo = a_hi + kBLo;
+          const uint64_t a_lo = a_hi + kALo, b_hi = a_hi + kBHi;
+          // Issuing one tcgen05.mma costs the issuing thread about 120 cycles whatever its
+          // size, which is more than a 128 x 128 x 16 product takes to execute.  The B_hi and
+          // B_lo tiles of a stage are adjacent in shared memory, so A_hi x [B_hi; B_lo] is ONE
+          // instruction of twice the width that yields hi*hi (columns 0..BN) and hi*lo
+          // (columns BN..2BN); lo*hi is added onto the second half.  Eight instructions per
+          // stage instead of twelve, and all three products of a chunk leave TMEM together.
 #pragma unroll
-          for (int ks = 0; ks < K_STEPS; ++ks)
-            ptx::mma_f16_ss(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
+          for (int ks = 0; ks < K_STEPS; ++ks) {
+            ptx::mma_f16_ss(acc_hh, a_hi + 2 * ks, b_hi + 2 * ks, IDESC2,
                             (!first_in_chunk || ks > 0) ? 1u : 0u);
-          if (last_in_chunk) ptx::tc_commit(ptx::smem_u32(&d0_full[b0]));
-          if (kb == 0) {
-            // this D1 buffer held the corrections of the tile before the previous one
-            ok = ptx::mbar_wait_poll(ptx::smem_u32(&d1_empty[b1]), ((tile_iter >> 1) & 1u) ^ 1u,
-                                     abort_flag, p.status, ptx::kErrWaitD1Empty);
-            if (!ok) break;
-            ptx::tc_fence_after();
+            ptx::mma_f16_ss(acc_hh + BN, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, 1u);
           }
-#pragma unroll
-          for (int ks = 0; ks < K_STEPS; ++ks)
-            ptx::mma_f16_ss(d1, a_lo + 2 * ks, b_hi + 2 * ks, IDESC, (kb > 0 || ks > 0) ? 1u : 0u);
-#pragma unroll
-          for (int ks = 0; ks < K_STEPS; ++ks)
-            ptx::mma_f16_ss(d1, a_hi + 2 * ks, b_lo + 2 * ks, IDESC, 1u);
+          if (last_in_chunk) ptx::tc_commit(ptx::smem_u32(&d0_full[b0]));
           ptx::tc_commit(ptx::smem_u32(&empty_bar[s]));
           if (last_in_chunk) ++chunk_idx;
           if (++s == STAGES) {
@@ -590,7 +589,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
             ph ^= 1u;
           }
         }
-        if (ok) ptx::tc_commit(ptx::smem_u32(&d1_full[b1]));
       }
     }
   } else if (!is_epilogue) {
@@ -688,9 +686,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
     const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
     const float lsi = p.lo_scale_inv;
 
-    uint32_t chunk_idx = 0, tile_iter = 0;
+    uint32_t chunk_idx = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+    for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const TileCoord tc = tile_coord<BN>(tile, p);
       float acc[CPT];
 #pragma unroll
@@ -705,39 +703,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
                                     p.status, ptx::kErrWaitD0Full, 64);
         if (!ok) break;
         ptx::tc_fence_after();
+        // running sum += hi*hi + (hi*lo + lo*hi) * 2^-11, both FP32 round-to-nearest adds
+        // outside the tensor core
+        const uint32_t t_hh = tmem_base + b0 * (2 * BN) + lane_addr + col_base;
 #pragma unroll
         for (int pc = 0; pc < CPT / 16; ++pc) {
-          uint32_t v[16];
-          ptx::tmem_ld_32x32b_x16(tmem_base + b0 * BN + lane_addr + col_base + pc * 16, v);
+          uint32_t v[16], w[16];
+          ptx::tmem_ld_32x32b_x16(t_hh + pc * 16, v);
+          ptx::tmem_ld_32x32b_x16(t_hh + BN + pc * 16, w);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[pc * 16 + i] += __uint_as_float(v[i]);
+          for (int i = 0; i < 16; ++i)
+            acc[pc * 16 + i] =
+                fmaf(__uint_as_float(w[i]), lsi, acc[pc * 16 + i] + __uint_as_float(v[i]));
         }
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&d0_empty[b0]));
       }
       if (!ok) break;
-
-      const uint32_t b1 = tile_iter & 1u;
-      ok = ptx::mbar_wait_backoff(ptx::smem_u32(&d1_full[b1]), (tile_iter >> 1) & 1u, abort_flag,
-                                  p.status, ptx::kErrWaitD1Full, 64);
-      if (!ok) break;
-      ptx::tc_fence_after();
-#pragma unroll
-      for (int pc = 0; pc < CPT / 16; ++pc) {
-        uint32_t v[16];
-        ptx::tmem_ld_32x32b_x16(tmem_base + Cfg::D1_COL + b1 * BN + lane_addr + col_base + pc * 16,
-                                v);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          acc[pc * 16 + i] = fmaf(__uint_as_float(v[i]), lsi, acc[pc * 16 + i]);
-      }
-      // D1 is in registers: the issuer may start the next tile's correction products
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&d1_empty[b1]));
 
       // C(row, col) = alpha * acc + beta * C(row, col)
       float *cp = cbase + static_cast<uint64_t>(tc.n0 + col_base) * p.ldc;
@@ -848,7 +832,7 @@ cudaError_t launch_fused_variant(const FusedGemmArgs &a, cudaStream_t stream) {
     const char *e = std::getenv("CUMPSGEMM_FUSED_DIAG");
     fp.diag = (e != nullptr) ? std::atoi(e) : 0;
   }
-  GemmKernelParams &p = fp.g;
+  GemmKernelParams p;
   p.c = a.c;
   p.c_array = nullptr;
   p.ldc = a.ldc;
@@ -882,7 +866,7 @@ cudaError_t launch_fused_variant(const FusedGemmArgs &a, cudaStream_t stream) {
   p.total_tiles = static_cast<uint32_t>(total);
   const unsigned grid = static_cast<unsigned>(
       total < static_cast<uint64_t>(num_sms[dev]) ? total : num_sms[dev]);
-  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(fp);
+  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(fp, p);
   return cudaGetLastError();
 }
 

@@ -427,10 +427,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                                const __grid_constant__ CUtensorMap map_a32,
                                const __grid_constant__ CUtensorMap map_b32,
                                const GemmKernelParams p32) {
-  if (p16.dyn->gemm_mode == CUMPSGEMM_TF32TCEC)
+  if (p16.dyn->gemm_mode == CUMPSGEMM_TF32TCEC) {
     pair_body<1>(map_a32, map_b32, p32);
-  else
+  } else {
     pair_body<0>(map_a16, map_b16, p16);
+  }
 }
 
 // Per device and kernel, once (any thread): shared-memory attribute and the number of
@@ -500,7 +501,7 @@ bool pair_prepare(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, CUt
     // Default: two stages (128 FP16 / 64 TF32 k values) per drain.  Measured at m=n=k=16384,
     // uniform(-1,1): residual 3.1e-7 / 2.8e-7 / 3.7e-7 / 6.5e-7 / 2.5e-6 / 1.9e-5 for 1 / 2 / 4 /
     // 8 / 32 / 256 stages per drain (FP32 cuBLAS SGEMM on the same inputs: 2.3e-6).
-    p.drain_chunk = (v >= 1) ? static_cast<uint32_t>(v) : 2u;
+    p.drain_chunk = static_cast<uint16_t>((v >= 1) ? (v > 0xffff ? 0xffff : v) : 2);
     // The first chunk of every tile is longer: while it accumulates, the epilogue warps are
     // still storing the previous tile, and the issuer would otherwise wait about 17,000 cycles
     // per tile for them to drain a short first chunk (measured: 5 % of a tile at k=16384, 18 %
@@ -517,7 +518,8 @@ bool pair_prepare(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, CUt
     uint32_t first_k = (k_total >= 8192u) ? 512u : (k_total >= 2048u ? 256u : 128u);
     if (kind != SplitKind::fp16) first_k /= 2u;
     const int fv = a.tuning.first_chunk;
-    p.first_chunk = (fv >= 1) ? static_cast<uint32_t>(fv) : first_k / k_per_stage;
+    const uint32_t first = (fv >= 1) ? static_cast<uint32_t>(fv) : first_k / k_per_stage;
+    p.first_chunk = static_cast<uint16_t>(first > 0xffffu ? 0xffffu : first);
     if (p.first_chunk < p.drain_chunk) p.first_chunk = p.drain_chunk;
   }
   const uint64_t total = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
