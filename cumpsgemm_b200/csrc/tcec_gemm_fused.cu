@@ -34,12 +34,19 @@
 // per drain chunk (the epilogue warps drain one while the tensor core fills the other).  Every
 // wait is bounded.  No TMA is used at all.
 //
-// What bounds it (measured with in-kernel time stamps, 128 x 128 tiles): the issuing thread
-// needs about 120 cycles per tcgen05.mma whatever its size (1,000 cycles per stage for eight
-// instructions against 770 cycles of tensor-core work), and a converter warp needs about
-// 2,400 cycles per stage (its loads share the L1 / shared-memory data path with its stores),
-// so a stage takes about 3,000 cycles: a quarter of the tensor-core rate, which is why the
-// dispatch uses this kernel only where the two-kernel path is bound by its HBM round trip.
+// What bounds it (cycle sums per role from a diagnostic build, 512 complex 256^3 products,
+// 128 x 128 tiles): a stage takes about 3,350 cycles.  A converter warp spends 2,200-2,400 of
+// them loading, converting and storing its share (about 900 are load latency, 600 the split
+// arithmetic and the stores), 100 on the fence and the arrival and 1,000 waiting for the
+// stage's shared memory: all sixteen warps work on the same stage, so latency and conversion
+// add up instead of overlapping.  The issuing thread is busy for 800 cycles per stage (eight
+// instructions, 770 cycles of tensor-core work) and waits for operands the rest of the time;
+// the epilogue warps drain for 590 and store for 380.  A quarter of the tensor-core rate, which
+// is why the dispatch uses this kernel only where the two-kernel path is bound by its HBM round
+// trip.  Two converter teams taking the stages in turn (one team's latency under the other's
+// conversion) were tried and measured slower (0.59 against 0.38 ms): three stages of 64 KiB
+// are all that fit, and with two of them being converted a team always needs the stage the
+// tensor core has only just received from the other team.
 //
 // Operand layouts the converters understand (anything else takes the pre-split path):
 //   kcontig  element (r, kk) of the real operand at src[r * ld + kk]      (A with op T, B with
@@ -87,14 +94,11 @@ struct FusedOperand {
 struct FusedParams {
   FusedOperand a, b;
   uint32_t k;      // K of the real (expanded) problem
-  // Diagnostic switches for timing experiments (environment variable CUMPSGEMM_FUSED_DIAG, 0 in
-  // production): bit 0 = converters use constants instead of loading the operands, bit 1 =
-  // converters skip the split arithmetic and the stores.  Results are then meaningless; the
-  // time that remains separates load latency, conversion work and the rest of the pipeline.
-  // The two tests also shape the generated code: they put the loads of a stage, its
-  // conversions and what precedes them into separate basic blocks, and the kernel measured
-  // 13 % faster with them than without (0.44 against 0.50 ms for 512 complex 256^3 products),
-  // so they stay.
+  // Diagnostic builds only (-DCUMPSGEMM_FUSED_DIAG_BUILD, never the library): bit 0 = the
+  // converters use constants instead of loading the operands, bit 1 = they skip the split
+  // arithmetic and the stores (environment variable CUMPSGEMM_FUSED_DIAG).  Results are then
+  // meaningless; the time that remains separates load latency, conversion work and the rest of
+  // the pipeline.  In the library the switches are the constant 0 and compile away.
   int diag;
 };
 // Every kernel parameter stays at or under 128 bytes: a larger struct is read through a pointer
@@ -460,6 +464,33 @@ __device__ __forceinline__ void convert_operand(const FusedOperand &o, const flo
     convert_cplx_a<ROWS>(o, src, row0, k0, kmax, scale, hi_base, lo_base, cw, lane, prefetch);
 }
 
+// Hints the operand tile (rows row0 .. row0 + rows_tile of the real operand, all of K) of one
+// batch entry into L2, one prefetch per 128-byte line, lines dealt out over `nthreads` threads.
+// Only addresses inside the operand are named.
+__device__ __forceinline__ void prefetch_operand_tile(const FusedOperand &o, uint32_t batch,
+                                                      uint32_t row0, uint32_t rows_tile,
+                                                      uint32_t k, uint32_t t, uint32_t nthreads) {
+  if (row0 >= o.rows) return;
+  const uint32_t rows = (o.rows - row0 < rows_tile) ? o.rows - row0 : rows_tile;
+  const float *base = o.src + static_cast<uint64_t>(batch) * o.stride;
+  uint32_t nseg, seg_len; // segments of seg_len contiguous floats, o.ld floats apart
+  if (o.layout == kLayoutKContig) {
+    nseg = rows;
+    seg_len = k;
+    base += static_cast<uint64_t>(row0) * o.ld;
+  } else {
+    nseg = (o.layout == kLayoutRContig) ? k : (k >> 1);
+    seg_len = rows;
+    base += row0;
+  }
+  const uint32_t lps = (seg_len + 31u) >> 5; // 128-byte steps per segment
+  const uint32_t total = nseg * lps;
+  for (uint32_t i = t; i < total; i += nthreads) {
+    const uint32_t seg = i / lps, j = i - seg * lps;
+    ptx::prefetch_l2(base + static_cast<uint64_t>(seg) * o.ld + (j << 5));
+  }
+}
+
 struct TileCoord {
   uint32_t batch;
   uint32_t m0, n0;
@@ -489,6 +520,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr uint32_t IDESC = ptx::make_idesc(0, BM, BN);
   constexpr int CPT = BN / 2;
+#ifdef CUMPSGEMM_FUSED_DIAG_BUILD
+  const int kdiag = fp.diag;
+#else
+  constexpr int kdiag = 0;
+#endif
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(
@@ -500,6 +536,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
   uint64_t *d0_empty = bars + 2 * STAGES + 2; // [2]
   uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
+  // tiles the issuing thread has started (read by the prefetching warps)
+  volatile uint32_t *tiles_started = reinterpret_cast<volatile uint32_t *>(tmem_base_ptr + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -515,6 +553,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
       ptx::mbar_init(ptx::smem_u32(&d0_empty[b]), NUM_EPI_WARPS);
     }
     *abort_flag = 0;
+    *tiles_started = 0;
     ptx::mbar_init_fence();
   }
   if (warp == MMA_WARP) {
@@ -546,7 +585,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
       constexpr uint64_t kALo = Cfg::A_TILE >> 4, kBHi = (2 * Cfg::A_TILE) >> 4;
       constexpr uint32_t IDESC2 = ptx::make_idesc(0, BM, 2 * BN);
       uint32_t s = 0, ph = 0, chunk_idx = 0;
+      uint32_t started = 0;
       for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        *tiles_started = ++started;
         uint32_t chunk_end = 0; // first stage after the current chunk
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
           const bool first_in_chunk = (kb == chunk_end);
@@ -589,6 +630,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
             ph ^= 1u;
           }
         }
+      }
+    } else if (warp > MMA_WARP) {
+      // The other three warps of the issuer's warpgroup pull the operand tiles of the CTA's
+      // NEXT tile into L2 while the current one is computed, so that the converters' loads find
+      // them there (a converter has one stage in flight and cannot look further ahead itself).
+      // They follow the issuing thread's tile count; a hint engine only: if it falls behind or
+      // gives up, nothing depends on it.
+      const uint32_t t = threadIdx.x - (MMA_WARP + 1) * 32;
+      constexpr uint32_t PF_THREADS = (NUM_THREADS / 32 - MMA_WARP - 1) * 32;
+      uint32_t it = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        ++it;
+        uint32_t polls = 0;
+        while (*tiles_started < it && !*abort_flag && ++polls < (1u << 22)) __nanosleep(256);
+        if (*tiles_started < it) break;
+        const uint32_t next = tile + gridDim.x;
+        if (next >= total_tiles) break;
+        const TileCoord tn = tile_coord<BN>(next, p);
+        prefetch_operand_tile(fp.a, tn.batch, tn.m0, BM, fp.k, t, PF_THREADS);
+        prefetch_operand_tile(fp.b, tn.batch, tn.n0, BN, fp.k, t, PF_THREADS);
       }
     }
   } else if (!is_epilogue) {
@@ -637,19 +698,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
           const uint32_t hi_addr = hi_tile + pl.st_off;
           if (o.layout == kLayoutKContig) {
             if (for_a) {
-              if (scaled) fast_kcontig<BM, true>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
-              else fast_kcontig<BM, false>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
+              if (scaled) fast_kcontig<BM, true>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, kdiag);
+              else fast_kcontig<BM, false>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, kdiag);
             } else {
-              if (scaled) fast_kcontig<BN, true>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
-              else fast_kcontig<BN, false>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
+              if (scaled) fast_kcontig<BN, true>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, kdiag);
+              else fast_kcontig<BN, false>(lp, 2 * o.ld, scale, hi_addr, lo_delta, pl, kdiag);
             }
           } else if (pl.active) {
             if (o.layout == kLayoutRContig) {
               if (scaled) fast_rcontig<true>(lp, o.ld, scale, hi_addr, lo_delta, pl);
               else fast_rcontig<false>(lp, o.ld, scale, hi_addr, lo_delta, pl);
             } else {
-              if (scaled) fast_cplx_a<true>(lp, o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
-              else fast_cplx_a<false>(lp, o.ld, scale, hi_addr, lo_delta, pl, fp.diag);
+              if (scaled) fast_cplx_a<true>(lp, o.ld, scale, hi_addr, lo_delta, pl, kdiag);
+              else fast_cplx_a<false>(lp, o.ld, scale, hi_addr, lo_delta, pl, kdiag);
             }
           }
         } else if (for_a) {
@@ -828,10 +889,10 @@ cudaError_t launch_fused_variant(const FusedGemmArgs &a, cudaStream_t stream) {
   fp.b.rows = a.n;
   fp.b.layout = a.layout_b;
   fp.k = a.k;
-  {
-    const char *e = std::getenv("CUMPSGEMM_FUSED_DIAG");
-    fp.diag = (e != nullptr) ? std::atoi(e) : 0;
-  }
+  fp.diag = 0;
+#ifdef CUMPSGEMM_FUSED_DIAG_BUILD
+  if (const char *e = std::getenv("CUMPSGEMM_FUSED_DIAG")) fp.diag = std::atoi(e);
+#endif
   GemmKernelParams p;
   p.c = a.c;
   p.c_array = nullptr;
