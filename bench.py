@@ -828,6 +828,53 @@ def run_sweep(args):
     h.destroy()
 
 
+def run_case(args):
+    """One small configuration alone (for profiler captures and quick timings; one JSON line
+    marked "case": true): --case sgemm | sgemm_batch | cgemm_batch with --n (m=n=k), --batch,
+    --mode, --beta, --steps, --warmup."""
+    import torch
+
+    from cumpsgemm_b200 import api
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    h = api.Handle()
+    h.use_current_torch_stream()
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    n, batch = args.n, (args.batch if args.case != "sgemm" else 1)
+    mode = api.ComputeMode[args.mode]
+    cplx = args.case == "cgemm_batch"
+    count = batch * n * n
+
+    def rnd():
+        x = torch.rand(count * (2 if cplx else 1), device=dev, generator=g) * 2 - 1
+        return torch.view_as_complex(x.view(-1, 2)) if cplx else x
+    a, b, c = rnd(), rnd(), rnd()
+    if args.case == "sgemm":
+        def call():
+            h.gemm(0, 0, n, n, n, 1.0, a, n, b, n, args.beta, c, n, mode)
+    else:
+        def call():
+            h.gemm_strided_batch(0, 0, n, n, n, 1.0, a, n, n * n, b, n, n * n, args.beta, c, n,
+                                 n * n, batch, mode)
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = (8.0 if cplx else 2.0) * batch * n ** 3
+    print(json.dumps({"case": True, "config": f"{args.case} {args.mode} batch={batch} m=n=k={n} "
+                      f"beta={args.beta}", "ms": ms, "tflops": flops / ms / 1e9,
+                      "steps": args.steps, "kernel_status": h.kernel_status()}), flush=True)
+    h.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -844,6 +891,9 @@ def main():
     ap.add_argument("--skip-batch", action="store_true", help="leave the batch-sharded block out")
     ap.add_argument("--sweep-large", action="store_true",
                     help="with --sweep: also the 8 x 8192^3 batch and the 65536 x 65536 x 8192 GEMM")
+    ap.add_argument("--case", default=None, choices=["sgemm", "sgemm_batch", "cgemm_batch"],
+                    help="run one small configuration alone (see run_case)")
+    ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--sweep", action="store_true",
                     help="run the other benchmark configurations (documentation runs)")
     args = ap.parse_args()
@@ -852,6 +902,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.sweep:
         run_sweep(args)
+        return
+    if args.case is not None:
+        run_case(args)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)
