@@ -784,6 +784,23 @@ def run_sweep(args):
         emit(config=f"cgemm strided batch {mode} batch={batch} m=n=k={s}", ms=ms,
              tflops=8.0 * batch * s ** 3 / ms / 1e9)
     del za, zb, zc
+    # the regimes the on-the-fly split kernel and split-K exist for: many small products, and
+    # few tiles with a long K
+    batch, s = 2048, 128
+    a = torch.rand(batch * s * s, device=dev, generator=g) * 2 - 1
+    b = torch.rand(batch * s * s, device=dev, generator=g) * 2 - 1
+    c = torch.zeros(batch * s * s, device=dev)
+    ms = timeit(lambda: h.gemm_strided_batch(0, 0, s, s, s, 1.0, a, s, s * s, b, s, s * s, 0.0, c, s,
+                                             s * s, batch, api.ComputeMode.FP16TCEC), 20)
+    emit(config=f"sgemm strided batch FP16TCEC batch={batch} m=n=k={s}", ms=ms,
+         tflops=2.0 * batch * s ** 3 / ms / 1e9)
+    m, k = 256, 65536
+    a = torch.rand(m * k, device=dev, generator=g) * 2 - 1
+    b = torch.rand(k * m, device=dev, generator=g) * 2 - 1
+    c = torch.zeros(m * m, device=dev)
+    ms = timeit(lambda: h.gemm(0, 0, m, m, k, 1.0, a, m, b, k, 0.0, c, m, api.ComputeMode.FP16TCEC), 20)
+    emit(config=f"sgemm FP16TCEC m=n={m} k={k} (split-K)", ms=ms, tflops=2.0 * m * m * k / ms / 1e9)
+    del a, b, c
     if args.sweep_large:
         # config 5a, one GPU's share at 8 GPUs: batch 8 of 8192^3, N(0,1), AUTO
         n, batch = 8192, 8
