@@ -283,16 +283,19 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
   // split-K partial sums: k_slices blocks of m x n floats per batch entry, behind the panels
   const std::size_t bytes_p_1 =
       (k_slices > 1) ? static_cast<std::size_t>(k_slices) * m_exp * n * sizeof(float) : 0;
+  // scratch of the pair kernel's tail split (once per call, behind everything else)
+  const std::size_t bytes_tail = use_pair ? pair_tail_scratch_bytes(h->num_sms) : 0;
   std::uint64_t chunk = std::max<std::uint64_t>(1, limit / (bytes_a_1 + bytes_b_1 + bytes_p_1));
   chunk = std::min<std::uint64_t>(chunk, batch);
   chunk = std::min<std::uint64_t>(chunk, 32768); // planes of a tensor map, tiles of a launch
-  if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1 + bytes_p_1))) {
+  if (!ensure_workspace(h, chunk * (bytes_a_1 + bytes_b_1 + bytes_p_1) + bytes_tail)) {
     log_error("failed to allocate the operand workspace");
     return CUBLAS_STATUS_ALLOC_FAILED;
   }
   char *ws_a = reinterpret_cast<char *>(h->workspace);
   char *ws_b = ws_a + chunk * bytes_a_1;
   float *ws_p = reinterpret_cast<float *>(ws_b + chunk * bytes_b_1);
+  float *ws_t = reinterpret_cast<float *>(reinterpret_cast<char *>(ws_p) + chunk * bytes_p_1);
 
   const bool prof = h->exp_stats.profiling_enabled;
   if (prof) h->exp_stats.profiler.start("gemm_kernel", h->cuda_stream);
@@ -370,6 +373,7 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
     g.tuning = h->tuning;
     g.k_slices = k_slices;
     g.partial = (k_slices > 1) ? ws_p : nullptr;
+    g.tail_partial = use_pair ? ws_t : nullptr;
     if (auto_kind)
       err = use_pair ? launch_tcec_gemm_pair_auto(g, h->cuda_stream)
                      : launch_tcec_gemm_auto(g, h->cuda_stream);

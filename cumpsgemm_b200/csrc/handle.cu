@@ -45,6 +45,8 @@ Tuning read_tuning_env() {
   t.fused = (fu == 0 || fu == 1) ? fu : -1;
   const int sk = as_int("CUMPSGEMM_SPLIT_K", -1);
   t.split_k = (sk >= 0) ? sk : -1;
+  const int ts = as_int("CUMPSGEMM_TAIL_SPLIT", -1);
+  t.tail_split = (ts >= 0) ? ts : -1;
   return t;
 }
 void log_warning(const std::string &s) {
@@ -88,7 +90,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
   ok &= cudaMalloc(&h->dyn_launch.flag_buffer, sizeof(int) * h->dyn_launch.flag_buffer_length) ==
         cudaSuccess;
   ok &= cudaMalloc(&h->dev_dyn_params, sizeof(DynParams) * h->dyn_params_length) == cudaSuccess;
-  ok &= cudaMalloc(&h->dev_status, 2 * sizeof(int)) == cudaSuccess; // status, wave counter
+  ok &= cudaMalloc(&h->dev_status, (2 + kPairTailCounters) * sizeof(int)) == cudaSuccess; // status, wave counter, tail-split counters
   ok &= cudaEventCreateWithFlags(&h->order_event, cudaEventDisableTiming) == cudaSuccess;
   const size_t scan_scratch_bytes = static_cast<size_t>(h->num_sms) * 8 * 24 * 2 + 16;
   ok &= cudaMalloc(&es.dev_scan_scratch, scan_scratch_bytes) == cudaSuccess;
@@ -103,7 +105,7 @@ extern "C" cublasStatus_t cuMpSGEMM_create(cuMpSGEMM_handle_t *const handle) {
   cudaMemsetAsync(es.dev_mode, 0, sizeof(int) * es.buffer_length, h->cuda_stream);
   cudaMemsetAsync(h->dyn_launch.flag_buffer, 0, sizeof(int) * h->dyn_launch.flag_buffer_length,
                   h->cuda_stream);
-  cudaMemsetAsync(h->dev_status, 0, 2 * sizeof(int), h->cuda_stream);
+  cudaMemsetAsync(h->dev_status, 0, (2 + kPairTailCounters) * sizeof(int), h->cuda_stream);
   cudaMemsetAsync(es.dev_scan_scratch, 0, scan_scratch_bytes, h->cuda_stream);
   configure_mode_buffer(h);
   init_flag_buffer(h);

@@ -82,6 +82,7 @@ struct Tuning {
   int pace = 1;
   int fused = -1;      // -1 = by rule
   int split_k = -1;    // CUMPSGEMM_SPLIT_K: 0 = never, -1 = by rule, n > 1 = that many slices
+  int tail_split = -1; // CUMPSGEMM_TAIL_SPLIT: 0 = never, -1 = by rule, n > 1 = at most n slices
 };
 Tuning read_tuning_env();
 
@@ -256,7 +257,17 @@ struct TcecGemmArgs {
   // slice the same whole number of 64-k-value units (0 or 1: no split).
   std::uint32_t k_slices = 1;
   float *partial = nullptr;
+  // Pair kernel only: scratch for the K-split of the last, partly filled wave of tiles
+  // (pair_tail_scratch_bytes() bytes) and kPairTailCounters zeroed device words behind
+  // `wave_counter`; null switches the tail split off.
+  float *tail_partial = nullptr;
 };
+// Device words the pair kernel's tail split needs behind the wave counter (two per tail tile).
+constexpr int kPairTailCounters = 256;
+// Bytes of `tail_partial` on a device with num_sms SMs: one 256 x 256 FP32 tile per CTA pair.
+inline std::size_t pair_tail_scratch_bytes(int num_sms) {
+  return static_cast<std::size_t>(num_sms / 2) * 256u * 256u * sizeof(float);
+}
 // Slices actually used when `wanted` are asked for a K loop of k_pad values.
 std::uint32_t split_k_slices(std::uint32_t k_pad, std::uint32_t wanted);
 // C = alpha * unscale * sum_s partial[s] + beta * C with the slices added in ascending order

@@ -178,6 +178,11 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity,
   return ok;
 }
 
+// Barrier `id` (1..15; 0 is __syncthreads) over `count` threads of the CTA (a multiple of 32).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // Hint: bring the cache line at p into L2.
 __device__ __forceinline__ void prefetch_l2(const void *p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");

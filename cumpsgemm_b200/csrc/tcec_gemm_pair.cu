@@ -87,9 +87,51 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t tile, const GemmKernelP
   return c;
 }
 
+// K-split of the last, partly filled wave.  With T tiles on C clusters the last wave has
+// T mod C tiles; when that is at most half of C, each of those tiles is cut into `slices` K
+// ranges that run on different clusters at the same time, so the wave takes 1/slices of a
+// tile's time instead of a whole one (m=n=k=4096: 256 tiles on 74 clusters = 3.46 waves, the
+// last 34 tiles are cut in two and the launch takes 3.5 tile times instead of 4).  Every slice
+// writes its plain FP32 partial sums to scratch memory and takes a ticket from the tile's
+// counter; the CTA that draws the last ticket adds the slices in ascending order (so the
+// result does not depend on which one that is) and runs the alpha / beta epilogue.  Nobody
+// waits for anybody, hence no assumption about which clusters are resident together.
+// Work item w of a launch: w < split_begin is tile w with its whole K loop; beyond that,
+// item split_begin + u is slice u % slices of tile split_begin + u / slices.
+struct PairTail {
+  float *partial;          // [tail tile][slice][CTA rank][256 columns][128 rows]
+  unsigned int *counters;  // [tail tile][CTA rank], zero at launch
+  uint32_t split_begin;    // first tile that is split (= total tiles when nothing is split)
+  uint32_t slices;         // K slices per split tile (1: nothing is split)
+  uint32_t slice_blocks;   // stages per slice (the last one may be shorter)
+  uint32_t work_items;     // split_begin + (total tiles - split_begin) * slices
+};
+
+struct WorkItem {
+  uint32_t tile, kb0, kbn, slice;
+};
+
+__device__ __forceinline__ WorkItem work_item(uint32_t w, const PairTail &t, uint32_t k_blocks) {
+  WorkItem x;
+  if (w < t.split_begin) {
+    x.tile = w;
+    x.kb0 = 0;
+    x.kbn = k_blocks;
+    x.slice = 0;
+  } else {
+    const uint32_t u = w - t.split_begin;
+    const uint32_t ti = u / t.slices;
+    x.tile = t.split_begin + ti;
+    x.slice = u - ti * t.slices;
+    x.kb0 = x.slice * t.slice_blocks;
+    x.kbn = min(t.slice_blocks, k_blocks - x.kb0);
+  }
+  return x;
+}
+
 template <int KIND>
 __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtensorMap &map_b,
-                                          const GemmKernelParams &p) {
+                                          const GemmKernelParams &p, const PairTail &tail) {
   constexpr int K_STEPS = ROW_BYTES / 32;
   constexpr int MY_MODE = (KIND == 0) ? CUMPSGEMM_FP16TCEC : CUMPSGEMM_TF32TCEC;
   constexpr uint32_t IDESC = ptx::make_idesc(KIND == 0 ? 0 : 2, 2 * BM_CTA, BN_PAIR);
@@ -109,6 +151,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
   uint64_t *d1_empty = bars + 2 * STAGES + 3;
   uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
+  volatile uint32_t *ticket_smem = reinterpret_cast<volatile uint32_t *>(tmem_base_ptr + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -116,7 +159,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
   const bool leader = (rank == 0);
   const uint32_t cluster_id = blockIdx.x >> 1;
   const uint32_t num_clusters = gridDim.x >> 1;
-  const uint32_t total_tiles = p.total_tiles;
+  const uint32_t work_items = tail.work_items;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -152,10 +195,11 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
     if (lane == 0) {
       uint32_t it = 0; // stage uses since kernel start, across tiles
       bool ok = true;
-      bool pace = leader && p.wave_counter != nullptr && total_tiles > num_clusters;
+      bool pace = leader && p.wave_counter != nullptr && work_items > num_clusters;
       uint32_t wave = 0;
-      for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++wave) {
-        const TileCoord tc = tile_coord(tile, p, rank);
+      for (uint32_t w = cluster_id; w < work_items && ok; w += num_clusters, ++wave) {
+        const WorkItem wi = work_item(w, tail, k_blocks);
+        const TileCoord tc = tile_coord(wi.tile, p, rank);
         const int za = static_cast<int>(tc.batch * 2u);
         const int nb0 = tc.n0 + static_cast<int>(rank) * 128; // this CTA's rows of the B tile
         if (pace) {
@@ -168,7 +212,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
           // then this cluster stops pacing for the rest of the launch, so clusters that are
           // not resident at the same time cost one time-out and never a wrong result.
           atomicAdd(p.wave_counter, 1u);
-          const uint32_t target = min(total_tiles, (wave + 1) * num_clusters);
+          const uint32_t target = min(work_items, (wave + 1) * num_clusters);
           const uint64_t t0 = ptx::globaltimer_ns();
           while (*reinterpret_cast<volatile unsigned int *>(p.wave_counter) < target) {
             if (ptx::globaltimer_ns() - t0 > 100000ull) {
@@ -178,7 +222,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
             __nanosleep(64);
           }
         }
-        for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (uint32_t kb = 0; kb < wi.kbn; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = ptx::mbar_wait_timed(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
@@ -190,7 +234,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
           const uint32_t st = ptx::smem_u32(smem + s * STAGE_BYTES);
           // coordinates: (element in the K block, row, plane * k_blocks + K block); each box
           // is one contiguous 16 KiB run of the K-blocked panel
-          const int zh = static_cast<int>(static_cast<uint32_t>(za) * k_blocks + kb);
+          const int zh = static_cast<int>(static_cast<uint32_t>(za) * k_blocks + wi.kb0 + kb);
           const int zl = zh + static_cast<int>(k_blocks);
           ptx::tma_load_3d_pair(st, &map_a, fb, 0, tc.m0, zh);
           ptx::tma_load_3d_pair(st + TILE_BYTES, &map_a, fb, 0, tc.m0, zl);
@@ -215,9 +259,9 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
         return kb == 0 || (kb >= first && (kb - first) % chunk == 0);
       };
       uint32_t it = 0, chunk_idx = 0, tile_iter = 0;
-      for (uint32_t tile = cluster_id; tile < total_tiles && ok;
-           tile += num_clusters, ++tile_iter) {
-        for (uint32_t kb = 0; kb < k_blocks && ok; ++kb, ++it) {
+      for (uint32_t w = cluster_id; w < work_items && ok; w += num_clusters, ++tile_iter) {
+        const uint32_t kbn = work_item(w, tail, k_blocks).kbn;
+        for (uint32_t kb = 0; kb < kbn && ok; ++kb, ++it) {
           const bool first_in_chunk = chunk_start(kb);
           const uint32_t s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -240,7 +284,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
           for (int ks = 0; ks < K_STEPS; ++ks)
             mma_pair<KIND>(d0, a_hi + 2 * ks, b_hi + 2 * ks, IDESC,
                            (!first_in_chunk || ks > 0) ? 1u : 0u);
-          const bool last_in_chunk = (kb + 1 == k_blocks) || chunk_start(kb + 1);
+          const bool last_in_chunk = (kb + 1 == kbn) || chunk_start(kb + 1);
           if (last_in_chunk) ptx::tc_commit_pair(ptx::smem_u32(d0_full), BOTH);
           if (kb == 0) {
             // D1 still holds the previous tile's corrections until its epilogue has read them.
@@ -275,10 +319,6 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
     const uint32_t col_base = half * CPT;
     const uint32_t d0_empty_leader = ptx::map_to_cta(ptx::smem_u32(d0_empty), 0);
     const uint32_t d1_empty_leader = ptx::map_to_cta(ptx::smem_u32(d1_empty), 0);
-    const uint32_t n_chunks =
-        1u + ((k_blocks > p.first_chunk)
-                  ? (k_blocks - p.first_chunk + p.drain_chunk - 1) / p.drain_chunk
-                  : 0u);
     const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
     const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
     const float br = p.beta_r, bi = p.beta_i;
@@ -288,8 +328,14 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
 
     uint32_t chunk_idx = 0, tile_iter = 0;
     bool ok = true;
-    for (uint32_t tile = cluster_id; tile < total_tiles && ok; tile += num_clusters, ++tile_iter) {
-      const TileCoord tc = tile_coord(tile, p, rank);
+    for (uint32_t w = cluster_id; w < work_items && ok; w += num_clusters, ++tile_iter) {
+      const WorkItem wi = work_item(w, tail, k_blocks);
+      const bool split = w >= tail.split_begin; // this item is one K slice of a tile
+      const uint32_t n_chunks =
+          1u + ((wi.kbn > p.first_chunk)
+                    ? (wi.kbn - p.first_chunk + p.drain_chunk - 1) / p.drain_chunk
+                    : 0u);
+      const TileCoord tc = tile_coord(wi.tile, p, rank);
       float acc[CPT];
 #pragma unroll
       for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
@@ -305,7 +351,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
       const uint32_t prefetch_at = (n_chunks > C_PREFETCH_LEAD) ? n_chunks - C_PREFETCH_LEAD : 0u;
 
       for (uint32_t c = 0; c < n_chunks; ++c, ++chunk_idx) {
-        if (read_c && c == prefetch_at) {
+        if (read_c && !split && c == prefetch_at) {
           // beta != 0: pull this warp's part of the C tile into L2 a few chunks before the
           // epilogue reads it (lane l fetches the line of columns l, l+32, ...)
 #pragma unroll
@@ -351,6 +397,31 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(d1_empty_leader);
+
+      if (split) {
+        // one K slice of a tile: park the partial sums, take a ticket, and go on to the
+        // epilogue only with the last ticket of this CTA's half of the tile
+        const uint32_t ti = wi.tile - tail.split_begin;
+        constexpr uint32_t HALF = BN_PAIR * BM_CTA; // floats of one CTA's 128 x 256 half
+        float *tbase = tail.partial + (static_cast<uint64_t>(ti) * tail.slices * 2u + rank) * HALF +
+                       quarter * 32u + static_cast<uint32_t>(lane);
+        float *mine = tbase + static_cast<uint64_t>(wi.slice) * 2u * HALF;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) __stcg(mine + (col_base + i) * BM_CTA, acc[i]);
+        __threadfence();
+        ptx::named_bar_sync(1, NUM_EPI_WARPS * 32);
+        if (warp == 4 && lane == 0) *ticket_smem = atomicAdd(tail.counters + ti * 2u + rank, 1u);
+        ptx::named_bar_sync(1, NUM_EPI_WARPS * 32);
+        if (*ticket_smem != tail.slices - 1u) continue;
+        __threadfence();
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) acc[i] = __ldcg(tbase + (col_base + i) * BM_CTA);
+        for (uint32_t sl = 1; sl < tail.slices; ++sl) {
+          const float *other = tbase + static_cast<uint64_t>(sl) * 2u * HALF;
+#pragma unroll
+          for (int i = 0; i < CPT; ++i) acc[i] += __ldcg(other + (col_base + i) * BM_CTA);
+        }
+      }
 
       // C(row, col) = alpha * acc + beta * C(row, col)
       // Columns go in groups of EPI_BATCH: all loads of a group are issued before its first
@@ -413,8 +484,9 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
 template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     tcec_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
-                          const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p) {
-  pair_body<KIND>(map_a, map_b, p);
+                          const __grid_constant__ CUtensorMap map_b, const GemmKernelParams p,
+                          const PairTail tail) {
+  pair_body<KIND>(map_a, map_b, p, tail);
 }
 
 // AUTO: both kinds' tensor maps and parameters travel with the launch; the device-side
@@ -426,11 +498,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                                const GemmKernelParams p16,
                                const __grid_constant__ CUtensorMap map_a32,
                                const __grid_constant__ CUtensorMap map_b32,
-                               const GemmKernelParams p32) {
+                               const GemmKernelParams p32, const PairTail tail16,
+                               const PairTail tail32) {
   if (p16.dyn->gemm_mode == CUMPSGEMM_TF32TCEC) {
-    pair_body<1>(map_a32, map_b32, p32);
+    pair_body<1>(map_a32, map_b32, p32, tail32);
   } else {
-    pair_body<0>(map_a16, map_b16, p16);
+    pair_body<0>(map_a16, map_b16, p16, tail16);
   }
 }
 
@@ -530,17 +603,53 @@ bool pair_prepare(const TcecGemmArgs &a, SplitKind kind, CUtensorMap *map_a, CUt
   return true;
 }
 
+// Plan of the tail split (see PairTail) for a launch on at most `max_clusters` clusters.  A
+// slice keeps at least 1024 k values, so that a slice's prologue and drain stay amortised.
+PairTail plan_tail(const TcecGemmArgs &a, SplitKind kind, const GemmKernelParams &p,
+                   uint32_t max_clusters) {
+  PairTail t;
+  t.partial = nullptr;
+  t.counters = nullptr;
+  t.split_begin = p.total_tiles;
+  t.slices = 1;
+  t.slice_blocks = p.k_blocks;
+  t.work_items = p.total_tiles;
+  if (a.tail_partial == nullptr || a.wave_counter == nullptr || a.tuning.tail_split == 0) return t;
+  const uint32_t rem = p.total_tiles % max_clusters;
+  if (rem == 0 || 2 * rem > max_clusters || 2 * rem > static_cast<uint32_t>(kPairTailCounters))
+    return t;
+  const uint32_t k_per_stage = ROW_BYTES / ((kind == SplitKind::fp16) ? 2u : 4u);
+  const uint32_t min_stages = 1024u / k_per_stage;
+  uint32_t slices = max_clusters / rem;
+  if (slices > p.k_blocks / min_stages) slices = p.k_blocks / min_stages;
+  if (slices > 8u) slices = 8u;
+  if (a.tuning.tail_split > 1 && slices > static_cast<uint32_t>(a.tuning.tail_split))
+    slices = static_cast<uint32_t>(a.tuning.tail_split);
+  if (slices < 2u) return t;
+  const uint32_t per = (p.k_blocks + slices - 1) / slices;
+  slices = (p.k_blocks + per - 1) / per; // no empty slice
+  if (slices < 2u) return t;
+  t.partial = a.tail_partial;
+  t.counters = a.wave_counter + 1;
+  t.split_begin = p.total_tiles - rem;
+  t.slices = slices;
+  t.slice_blocks = per;
+  t.work_items = t.split_begin + rem * slices;
+  return t;
+}
+
 // Pacing pays when tiles are long (the drift it removes is 2 % of a tile) and clusters share
 // panel rows; for short tiles a barrier per tile costs more than it saves.
-cudaError_t pair_pacing(const TcecGemmArgs &a, uint32_t clusters, GemmKernelParams *p,
-                        cudaStream_t stream) {
-  if (a.wave_counter != nullptr && p->total_tiles > clusters && p->k_blocks >= kPaceMinStages &&
-      a.tuning.pace != 0) {
-    const cudaError_t me = cudaMemsetAsync(a.wave_counter, 0, sizeof(unsigned int), stream);
-    if (me != cudaSuccess) return me;
-    p->wave_counter = a.wave_counter;
-  }
-  return cudaSuccess;
+bool wants_pacing(const TcecGemmArgs &a, uint32_t clusters, const GemmKernelParams &p,
+                  const PairTail &t) {
+  return a.wave_counter != nullptr && t.work_items > clusters && p.k_blocks >= kPaceMinStages &&
+         a.tuning.pace != 0;
+}
+
+// The wave counter and the tail-split counters behind it start every launch at zero.
+cudaError_t reset_counters(const TcecGemmArgs &a, bool tail, cudaStream_t stream) {
+  return cudaMemsetAsync(a.wave_counter, 0,
+                         sizeof(unsigned int) * (tail ? 1 + kPairTailCounters : 1), stream);
 }
 
 template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t stream) {
@@ -548,15 +657,20 @@ template <int KIND> cudaError_t launch_pair(const TcecGemmArgs &a, cudaStream_t 
   int max_clusters = 1;
   const cudaError_t se = pair_setup<KIND>(kernel, &max_clusters);
   if (se != cudaSuccess) return se;
+  constexpr SplitKind kind = KIND == 0 ? SplitKind::fp16 : SplitKind::tf32;
   CUtensorMap map_a, map_b;
   GemmKernelParams p;
-  if (!pair_prepare(a, KIND == 0 ? SplitKind::fp16 : SplitKind::tf32, &map_a, &map_b, &p))
-    return cudaErrorInvalidValue;
+  if (!pair_prepare(a, kind, &map_a, &map_b, &p)) return cudaErrorInvalidValue;
+  const PairTail tail = plan_tail(a, kind, p, static_cast<uint32_t>(max_clusters));
   const uint32_t clusters =
-      p.total_tiles < static_cast<uint32_t>(max_clusters) ? p.total_tiles : max_clusters;
-  const cudaError_t pe = pair_pacing(a, clusters, &p, stream);
-  if (pe != cudaSuccess) return pe;
-  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+      tail.work_items < static_cast<uint32_t>(max_clusters) ? tail.work_items : max_clusters;
+  const bool pace = wants_pacing(a, clusters, p, tail);
+  if (pace) p.wave_counter = a.wave_counter;
+  if (pace || tail.slices > 1) {
+    const cudaError_t me = reset_counters(a, tail.slices > 1, stream);
+    if (me != cudaSuccess) return me;
+  }
+  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p, tail);
   return cudaGetLastError();
 }
 
@@ -578,14 +692,21 @@ cudaError_t launch_tcec_gemm_pair_auto(const TcecGemmArgs &a, cudaStream_t strea
   if (!pair_prepare(a, SplitKind::fp16, &a16, &b16, &p16) ||
       !pair_prepare(a, SplitKind::tf32, &a32, &b32, &p32))
     return cudaErrorInvalidValue;
-  const uint32_t clusters =
-      p16.total_tiles < static_cast<uint32_t>(max_clusters) ? p16.total_tiles : max_clusters;
+  const PairTail t16 = plan_tail(a, SplitKind::fp16, p16, static_cast<uint32_t>(max_clusters));
+  const PairTail t32 = plan_tail(a, SplitKind::tf32, p32, static_cast<uint32_t>(max_clusters));
+  // one grid for whichever kind runs: the larger of the two work lists, capped at what fits
+  uint32_t clusters = t16.work_items > t32.work_items ? t16.work_items : t32.work_items;
+  if (clusters > static_cast<uint32_t>(max_clusters)) clusters = max_clusters;
   // pacing depends on the K loop length, which differs by kind: one counter serves whichever runs
-  cudaError_t pe = pair_pacing(a, clusters, &p16, stream);
-  if (pe == cudaSuccess && p16.wave_counter == nullptr) pe = pair_pacing(a, clusters, &p32, stream);
-  else if (pe == cudaSuccess) p32.wave_counter = a.wave_counter;
-  if (pe != cudaSuccess) return pe;
-  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(a16, b16, p16, a32, b32, p32);
+  const bool pace16 = wants_pacing(a, clusters, p16, t16), pace32 = wants_pacing(a, clusters, p32, t32);
+  if (pace16) p16.wave_counter = a.wave_counter;
+  if (pace32) p32.wave_counter = a.wave_counter;
+  const bool tail = t16.slices > 1 || t32.slices > 1;
+  if (pace16 || pace32 || tail) {
+    const cudaError_t me = reset_counters(a, tail, stream);
+    if (me != cudaSuccess) return me;
+  }
+  kernel<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(a16, b16, p16, a32, b32, p32, t16, t32);
   return cudaGetLastError();
 }
 

@@ -583,3 +583,80 @@ def test_split_k_forced_uneven_slices_complex_and_batches(handle, oracle, slices
         assert handle.kernel_status() == 0
     finally:
         _split_k_env(handle, None)
+
+
+class _PairEnv:
+    """Force the CTA-pair kernel and set the tail-split switch for the calls inside."""
+
+    def __init__(self, handle, tail_split):
+        self.handle, self.tail_split = handle, tail_split
+
+    def __enter__(self):
+        os.environ["CUMPSGEMM_TILE_N"] = "256"
+        os.environ["CUMPSGEMM_PAIR"] = "1"
+        if self.tail_split is not None:
+            os.environ["CUMPSGEMM_TAIL_SPLIT"] = str(self.tail_split)
+        self.handle.reload_tuning_env()
+
+    def __exit__(self, *exc):
+        for name in ("CUMPSGEMM_TILE_N", "CUMPSGEMM_PAIR", "CUMPSGEMM_TAIL_SPLIT"):
+            os.environ.pop(name, None)
+        self.handle.reload_tuning_env()
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 2048, 4096),    # 32 tiles, no full wave: every tile in two slices
+                                   (3072, 1792, 2048),    # 84 tiles = one full wave + 10 split in two
+                                   (512, 512, 8192 + 64)])  # 4 tiles in eight uneven slices
+def test_pair_kernel_tail_split(handle, oracle, m, n, k):
+    """The last, partly filled wave of CTA-pair tiles is cut into K slices that run on otherwise
+    idle clusters; the CTA that finishes last adds the slices in ascending order.  The result is
+    right, the same on every run, and differs from the unsplit one only by summation order."""
+    torch = _torch()
+    a, b = oracle.gen_uniform(31, m * k), oracle.gen_uniform(32, k * n)
+    c0 = oracle.gen_uniform(33, m * n)
+    da, db = _dev(a), _dev(b)
+    truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a, m, b, k, 0.5, c0, m)
+    for mode in (FP16TCEC, TF32TCEC):
+        outs = []
+        with _PairEnv(handle, None):
+            for rep in range(3):
+                dc = _dev(c0.copy())
+                assert handle.gemm(N, N, m, n, k, 1.0, da, m, db, k, 0.5, dc, m, mode) == 0
+                outs.append(dc)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        assert oracle.residual(truth, outs[0].cpu().numpy(), m) < oracle.error_threshold(True, k)
+        with _PairEnv(handle, 0):
+            dc = _dev(c0.copy())
+            assert handle.gemm(N, N, m, n, k, 1.0, da, m, db, k, 0.5, dc, m, mode) == 0
+        assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+        assert not torch.equal(dc, outs[0])          # the split really happened
+        assert (dc - outs[0]).abs().max().item() < 1e-3
+    assert handle.kernel_status() == 0
+
+
+def test_pair_kernel_tail_split_complex_scaling_and_auto(handle, oracle):
+    """Tail split with complex alpha / beta (the last CTA's epilogue works on the summed
+    interleaved rows), with FP16TCEC_SCALING (un-scaling in that epilogue) and through the
+    one-launch AUTO kernel (the split plan differs by kind)."""
+    torch = _torch()
+    with _PairEnv(handle, None):
+        r = _run_complex(handle, oracle, N, N, 512, 2048, 1024, FP16TCEC, 0.5 - 1.5j, -0.25 + 2j, seed=41)
+        assert r < oracle.error_threshold(True, 1024)
+        m, n, k = 1024, 2048, 2048
+        a = (oracle.gen_uniform(42, m * k) * np.float32(2.0 ** -20)).astype(np.float32)
+        b = (oracle.gen_uniform(43, k * n) * np.float32(2.0 ** -18)).astype(np.float32)
+        c0 = np.zeros(m * n, dtype=np.float32)
+        truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c0, m)
+        da, db = _dev(a), _dev(b)
+        dc = _dev(c0.copy())
+        assert handle.gemm(N, N, m, n, k, 1.0, da, m, db, k, 0.0, dc, m, SCALING) == 0
+        assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+        for rep in range(2):
+            dca = _dev(c0.copy())
+            ia = handle.exp_stats_ext(m, k, da, m)
+            ib = handle.exp_stats_ext(k, n, db, k)
+            st = handle.gemm_strided_batch_with_stats(N, N, m, n, k, 1.0, da, m, 0, db, k, 0, 0.0, dca,
+                                                      m, 0, 1, AUTO, ia, ib)
+            assert st == 0
+            assert oracle.residual(truth, dca.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    assert handle.kernel_status() == 0
