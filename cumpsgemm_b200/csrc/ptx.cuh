@@ -183,6 +183,18 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute may start while the kernel before it in the stream still runs; griddep_wait()
+// returns once that kernel has completed and its writes are visible (a no-op for a kernel
+// launched the ordinary way).  griddep_launch_dependents() in the earlier kernel lets the later
+// one be scheduled as soon as every CTA of the earlier one has issued it or exited.
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Hint: bring the cache line at p into L2.
 __device__ __forceinline__ void prefetch_l2(const void *p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");

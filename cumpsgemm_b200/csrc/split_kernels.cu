@@ -359,6 +359,9 @@ struct SplitJob {
 template <int KIND, bool VEC>
 __global__ void __launch_bounds__(THREADS, VEC ? 5 : 6) split_dual_kernel(const SplitJob a, const SplitJob b) {
   __shared__ float tile[TILE][TILE + 1]; // transposing staging tile shared by all paths
+  // the GEMM kernel that follows may be scheduled while this one drains: its prologue does not
+  // depend on the panels, and its first panel load waits for this grid to complete
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t blocks_a = a.gx * a.gy * a.gz;
   uint32_t id = blockIdx.x;
   const SplitJob &j = (id < blocks_a) ? a : b;
@@ -375,6 +378,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(THREADS, VEC ? 5 : 6)
     split_dual_auto_kernel(const SplitJob a, const SplitJob b) {
   __shared__ float tile[TILE][TILE + 1];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // see split_dual_kernel
   const uint32_t blocks_a = a.gx * a.gy * a.gz;
   uint32_t id = blockIdx.x;
   const SplitJob &j = (id < blocks_a) ? a : b;

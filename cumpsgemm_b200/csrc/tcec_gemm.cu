@@ -132,6 +132,9 @@ __device__ __forceinline__ void tcec_gemm_body(const CUtensorMap &map_a, const C
   if (warp == 0) {
     // ================================================================ TMA producer
     if (lane == 0) {
+      // launched with programmatic serialization behind the split pass: everything up to here
+      // ran while that pass was still draining; the panels are complete after this
+      ptx::griddep_wait();
       const int za = static_cast<int>(batch_id * (EC ? 2u : 1u));
       for (uint32_t kb = 0; kb < k_blocks; ++kb) {
         const uint32_t s = kb % STAGES;
@@ -470,6 +473,25 @@ template <int TAG, class Kernel> cudaError_t smem_setup(Kernel kernel, int smem_
   return setup_error[dev];
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while the
+// kernel before it in the stream (the split pass) is still draining; the producer's
+// griddep_wait() orders the first panel load behind that kernel's completion.
+template <class Kernel, class... Args>
+cudaError_t launch_after_split(Kernel kernel, unsigned grid, int smem_bytes, cudaStream_t stream,
+                               Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int KIND, int BN, bool EC>
 cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   using Cfg = TileCfg<BN, EC>;
@@ -482,8 +504,7 @@ cudaError_t launch_variant(const TcecGemmArgs &a, cudaStream_t stream) {
   if (!prepare_variant<BN, EC>(a, KIND == 0 ? SplitKind::fp16 : SplitKind::tf32, &map_a, &map_b, &p,
                                &grid))
     return cudaErrorInvalidValue;
-  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(map_a, map_b, p);
-  return cudaGetLastError();
+  return launch_after_split(kernel, grid, Cfg::SMEM_BYTES, stream, map_a, map_b, p);
 }
 
 template <int BN> cudaError_t launch_auto_variant(const TcecGemmArgs &a, cudaStream_t stream) {
@@ -497,8 +518,7 @@ template <int BN> cudaError_t launch_auto_variant(const TcecGemmArgs &a, cudaStr
   if (!prepare_variant<BN, true>(a, SplitKind::fp16, &a16, &b16, &p16, &grid) ||
       !prepare_variant<BN, true>(a, SplitKind::tf32, &a32, &b32, &p32, &grid))
     return cudaErrorInvalidValue;
-  kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(a16, b16, p16, a32, b32, p32);
-  return cudaGetLastError();
+  return launch_after_split(kernel, grid, Cfg::SMEM_BYTES, stream, a16, b16, p16, a32, b32, p32);
 }
 
 template <int KIND, bool EC> cudaError_t launch_by_tile(const TcecGemmArgs &a, cudaStream_t s) {
