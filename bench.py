@@ -432,7 +432,7 @@ def batch_sharded_block(torch, dist, device, sharded, rank, world):
         "scaling": "strong", "batches_per_rank": nb, "ms": ms,
         "tflops": 8.0 * total * s ** 3 / ms / 1e9,
         "sampled_batch_residual": worst(res), "threshold": 2.0 ** -23 * s ** 0.5,
-        "collectives": "2 all-reduces per operand (max exponent) when world > 1"}
+        "collectives": "one 64-byte all-gather (both operands' maximum exponents) when world > 1"}
     del za, zb, zc
     # real 8 x 8192^3 per rank, N(0,1), AUTO; weak scaling
     n, nb = 8192, 8
@@ -452,8 +452,8 @@ def batch_sharded_block(torch, dist, device, sharded, rank, world):
         "scaling": "weak", "batches_per_rank": nb, "ms": ms,
         "tflops": 2.0 * nb * world * n ** 3 / ms / 1e9,
         "sampled_batch_residual": worst(res), "threshold": 2.0 ** -23 * n ** 0.5,
-        "collectives": "3 all-reduces per operand (max exponent, counters of both stages) "
-                       "when world > 1"}
+        "collectives": "two 64-byte all-gathers (both operands' slot words after each statistics "
+                       "stage) when world > 1"}
     del a, b, c
     return out
 

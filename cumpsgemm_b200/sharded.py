@@ -12,8 +12,9 @@ the inner loop:
 
 For ``AUTO`` and ``FP16TCEC_SCALING`` the reference's decision and scale factor
 cover the whole operand (``src/exp_stats.cu:81-82,163-165``), so the statistics
-slots are all-reduced between the stages (max of the exponent bits, sums of the
-two counters); every rank then takes the same decision as a 1-GPU run would.
+slots are combined over the ranks between the stages (max of the exponent bits, sums of
+the two counters; one small all-gather per stage for both operands together); every rank
+then takes the same decision as a 1-GPU run would.
 """
 from __future__ import annotations
 
@@ -56,7 +57,6 @@ class ShardedGemm:
         self.torch = torch
         self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self._words = None
 
     # ------------------------------------------------------------------ statistics
     def _global_rank(self, group_rank: int) -> int:
@@ -64,61 +64,80 @@ class ShardedGemm:
             return group_rank
         return self.dist.get_global_rank(self.group, group_rank)
 
-    def _allreduce_slot(self, stats_id: int, device) -> None:
-        """max over ranks of word 0 (exponent bits), sum over ranks of words 1..2 (counters)."""
-        if self.world_size == 1:
-            return
+    def _export(self, sids, device):
+        """[len(sids), 4] int64 on `device`: the exported words of the slots."""
+        torch = self.torch
+        w = torch.zeros(len(sids), 4, dtype=torch.int64, device=device)
+        for i, sid in enumerate(sids):
+            self.handle.exp_stats_export(sid, w[i])
+        return w
+
+    def _gather(self, w):
+        """[world, ...] stack of every rank's `w` (one collective, whatever the slot count)."""
         torch, dist = self.torch, self.dist
-        if self._words is None or self._words.device != device:
-            self._words = torch.zeros(4, dtype=torch.int64, device=device)
-        w = self._words
-        self.handle.exp_stats_export(stats_id, w)
-        dist.all_reduce(w[0:1], op=dist.ReduceOp.MAX, group=self.group)
-        dist.all_reduce(w[1:3], op=dist.ReduceOp.SUM, group=self.group)
-        self.handle.exp_stats_import(stats_id, w)
+        w = w.contiguous()
+        out = torch.empty((self.world_size,) + tuple(w.shape), dtype=w.dtype, device=w.device)
+        try:
+            dist.all_gather_into_tensor(out, w, group=self.group)
+        except (RuntimeError, NotImplementedError):   # a backend without the flat form
+            parts = [torch.empty_like(w) for _ in range(self.world_size)]
+            dist.all_gather(parts, w, group=self.group)
+            out = torch.stack(parts)
+        return out
+
+    def _global_stats(self, operands, full: bool):
+        """Statistics slots of several operands whose content equals what one GPU holding the
+        whole operands would compute.  operands: (m, n, ptr, ld, batch_size, stride, replicated)
+        with `replicated` = every rank holds the same full operand (no reduction needed).
+        full = False: maximum exponent only (FP16TCEC_SCALING).  All operands share the
+        collectives: one all-gather of the slot words per stage, reduced locally (max over ranks
+        of word 0, the exponent bits; sum over ranks of words 1..2, the counters)."""
+        h = self.handle
+        sids = [h.exp_stats_begin() for _ in operands]
+        for sid, o in zip(sids, operands):
+            h.exp_stats_stage(1 if full else 3, sid, *o[:6])
+        shared = [sid for sid, o in zip(sids, operands) if not o[6]] if self.world_size > 1 else []
+        device = operands[0][2].device
+        if shared:
+            w = self._export(shared, device)
+            g = self._gather(w)
+            w[:, 0] = g[:, :, 0].amax(dim=0)
+            if full:
+                w[:, 1:3] = g[:, :, 1:3].sum(dim=0)
+            for i, sid in enumerate(shared):
+                h.exp_stats_import(sid, w[i])
+        if not full:
+            return sids
+        for sid in sids:
+            h.exp_stats_decide(1, sid)
+        # After decision 1 the counters are either zero (undecided: stage 2 recounts) or already
+        # global (decided: stage 2 is skipped on the device).  Only what stage 2 adds locally may
+        # be summed over the ranks.
+        base = self._export(shared, device) if shared else None
+        for sid, o in zip(sids, operands):
+            h.exp_stats_stage(2, sid, *o[:6])
+        if shared:
+            now = self._export(shared, device)
+            delta = self._gather(now[:, 1:3] - base[:, 1:3]).sum(dim=0)
+            now[:, 1:3] = base[:, 1:3] + delta
+            for i, sid in enumerate(shared):
+                h.exp_stats_import(sid, now[i])
+        for sid in sids:
+            h.exp_stats_decide(2, sid)
+        return sids
 
     def global_exp_stats(self, m, n, ptr, ld, batch_size=1, stride=0, replicated=False) -> int:
-        """Statistics slot whose content equals what one GPU holding the whole operand would
-        compute.  `replicated`: every rank holds the same full operand (no reduction needed)."""
-        h = self.handle
-        sid = h.exp_stats_begin()
-        h.exp_stats_stage(1, sid, m, n, ptr, ld, batch_size, stride)
-        if not replicated:
-            self._allreduce_slot(sid, ptr.device)
-        h.exp_stats_decide(1, sid)
-        if replicated or self.world_size == 1:
-            h.exp_stats_stage(2, sid, m, n, ptr, ld, batch_size, stride)
-        else:
-            # After decision 1 the counters are either zero (undecided: stage 2 recounts) or
-            # already global (decided: stage 2 is skipped on the device).  Only what stage 2
-            # adds locally may be summed over the ranks.
-            torch, dist = self.torch, self.dist
-            w = self._words
-            h.exp_stats_export(sid, w)
-            base = w.clone()
-            h.exp_stats_stage(2, sid, m, n, ptr, ld, batch_size, stride)
-            h.exp_stats_export(sid, w)
-            delta = w[1:3] - base[1:3]
-            dist.all_reduce(delta, op=dist.ReduceOp.SUM, group=self.group)
-            w[1:3] = base[1:3] + delta
-            h.exp_stats_import(sid, w)
-        h.exp_stats_decide(2, sid)
-        return sid
+        """Statistics slot (both stages and decisions) of one operand spread over the ranks."""
+        return self._global_stats([(m, n, ptr, ld, batch_size, stride, replicated)], True)[0]
 
     def global_exp_max(self, m, n, ptr, ld, batch_size=1, stride=0, replicated=False) -> int:
-        h = self.handle
-        sid = h.exp_stats_begin()
-        h.exp_stats_stage(3, sid, m, n, ptr, ld, batch_size, stride)
-        if not replicated:
-            self._allreduce_slot(sid, ptr.device)
-        return sid
+        """Maximum-exponent slot of one operand spread over the ranks."""
+        return self._global_stats([(m, n, ptr, ld, batch_size, stride, replicated)], False)[0]
 
-    def _stats_for(self, mode, op, rows, cols, ptr, ld, batch, stride, replicated):
+    @staticmethod
+    def _operand(op, rows, cols, ptr, ld, batch, stride, replicated):
         sm, sn = (rows, cols) if op == CUBLAS_OP_N else (cols, rows)
-        stride_arg = stride if batch > 1 else 0
-        if mode == ComputeMode.AUTO:
-            return self.global_exp_stats(sm, sn, ptr, ld, batch, stride_arg, replicated)
-        return self.global_exp_max(sm, sn, ptr, ld, batch, stride_arg, replicated)
+        return (sm, sn, ptr, ld, batch, stride if batch > 1 else 0, replicated)
 
     # ------------------------------------------------------------------ batch partition
     def gemm_strided_batch_local(self, op_A, op_B, m, n, k, alpha, A, lda, stridea, B, ldb,
@@ -128,8 +147,10 @@ class ShardedGemm:
         mode = ComputeMode(mode)
         h = self.handle
         if mode in (ComputeMode.AUTO, ComputeMode.FP16TCEC_SCALING):
-            ida = self._stats_for(mode, op_A, m, k, A, lda, local_batch_count, stridea, False)
-            idb = self._stats_for(mode, op_B, k, n, B, ldb, local_batch_count, strideb, False)
+            ida, idb = self._global_stats(
+                [self._operand(op_A, m, k, A, lda, local_batch_count, stridea, False),
+                 self._operand(op_B, k, n, B, ldb, local_batch_count, strideb, False)],
+                mode == ComputeMode.AUTO)
             return h.gemm_strided_batch_with_stats(op_A, op_B, m, n, k, alpha, A, lda, stridea, B,
                                                    ldb, strideb, beta, Cmat, ldc, stridec,
                                                    local_batch_count, mode, ida, idb)
@@ -149,8 +170,10 @@ class ShardedGemm:
         if broadcast_A and self.world_size > 1:
             self.dist.broadcast(A, src=self._global_rank(root), group=self.group)
         if mode in (ComputeMode.AUTO, ComputeMode.FP16TCEC_SCALING):
-            ida = self._stats_for(mode, op_A, m, k, A, lda, 1, 0, True)
-            idb = self._stats_for(mode, op_B, k, n_local, B_local, ldb, 1, 0, False)
+            ida, idb = self._global_stats(
+                [self._operand(op_A, m, k, A, lda, 1, 0, True),
+                 self._operand(op_B, k, n_local, B_local, ldb, 1, 0, False)],
+                mode == ComputeMode.AUTO)
             return h.gemm_strided_batch_with_stats(op_A, op_B, m, n_local, k, alpha, A, lda, 0,
                                                    B_local, ldb, 0, beta, C_local, ldc, 0, 1,
                                                    mode, ida, idb)
