@@ -131,6 +131,7 @@ __global__ void init_flag_buffer_kernel(int *flag) {
 // inverse of what was applied.
 __global__ void dyn_params_kernel(DynParams *out, const int *flag, const float *max_a,
                                   const float *max_b) {
+  CUMPSGEMM_CHAINED_KERNEL_ENTRY();
   const int f = *flag;
   const float ma = *max_a, mb = *max_b;
   const bool sa = flag_scale_a(f) && ma != 0.f;
@@ -146,6 +147,7 @@ __global__ void dyn_params_kernel(DynParams *out, const int *flag, const float *
 __global__ void flag_and_dyn_params_kernel(DynParams *out, int *flag, const int *mode_a,
                                            const int *mode_b, const float *max_a,
                                            const float *max_b) {
+  CUMPSGEMM_CHAINED_KERNEL_ENTRY();
   const int pa = *mode_a, pb = *mode_b;
   int f;
   if (pa == CUMPSGEMM_TF32TCEC || pb == CUMPSGEMM_TF32TCEC) {
@@ -225,9 +227,10 @@ DynParams *prepare_dyn_params(cuMpSGEMM_handle *h, unsigned flag_id, unsigned st
                               unsigned stats_id_b) {
   DynParams *slot = h->dev_dyn_params + h->dyn_params_next;
   h->dyn_params_next = (h->dyn_params_next + 1) % h->dyn_params_length;
-  dyn_params_kernel<<<1, 1, 0, h->cuda_stream>>>(slot, h->dyn_launch.flag_buffer + flag_id,
-                                                 h->exp_stats.dev_max + stats_id_a,
-                                                 h->exp_stats.dev_max + stats_id_b);
+  launch_chained(dyn_params_kernel, 1, 1, 0, h->cuda_stream, slot,
+                 static_cast<const int *>(h->dyn_launch.flag_buffer + flag_id),
+                 static_cast<const float *>(h->exp_stats.dev_max + stats_id_a),
+                 static_cast<const float *>(h->exp_stats.dev_max + stats_id_b));
   return slot;
 }
 
@@ -235,10 +238,12 @@ DynParams *prepare_dyn_params_from_stats(cuMpSGEMM_handle *h, unsigned flag_id,
                                          unsigned stats_id_a, unsigned stats_id_b) {
   DynParams *slot = h->dev_dyn_params + h->dyn_params_next;
   h->dyn_params_next = (h->dyn_params_next + 1) % h->dyn_params_length;
-  flag_and_dyn_params_kernel<<<1, 1, 0, h->cuda_stream>>>(
-      slot, h->dyn_launch.flag_buffer + flag_id, h->exp_stats.dev_mode + stats_id_a,
-      h->exp_stats.dev_mode + stats_id_b, h->exp_stats.dev_max + stats_id_a,
-      h->exp_stats.dev_max + stats_id_b);
+  launch_chained(flag_and_dyn_params_kernel, 1, 1, 0, h->cuda_stream, slot,
+                 h->dyn_launch.flag_buffer + flag_id,
+                 static_cast<const int *>(h->exp_stats.dev_mode + stats_id_a),
+                 static_cast<const int *>(h->exp_stats.dev_mode + stats_id_b),
+                 static_cast<const float *>(h->exp_stats.dev_max + stats_id_a),
+                 static_cast<const float *>(h->exp_stats.dev_max + stats_id_b));
   return slot;
 }
 

@@ -436,6 +436,7 @@ struct DualScan {
 __global__ void __launch_bounds__(THREADS, 8)
     fused_stage1_dual_kernel(const DualScan d, float ignore_thr, float uf_thr, float tolerance,
                              ScanPartial *partials, unsigned int *tickets) {
+  CUMPSGEMM_CHAIN_HEAD_ENTRY(); // stage 2 may be scheduled while this grid drains
   const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
   const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
   const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
@@ -446,6 +447,7 @@ __global__ void __launch_bounds__(THREADS, 8)
 __global__ void __launch_bounds__(THREADS, 8)
     fused_stage2_dual_kernel(const DualScan d, float half_ignore_thr, float half_uf_thr,
                              float tolerance, ScanPartial *partials, unsigned int *tickets) {
+  CUMPSGEMM_CHAINED_KERNEL_ENTRY(); // launched behind stage 1: its results are complete after this
   const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
   const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
   const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
@@ -455,6 +457,7 @@ __global__ void __launch_bounds__(THREADS, 8)
 
 __global__ void __launch_bounds__(THREADS, 8)
     fused_max_dual_kernel(const DualScan d, ScanPartial *partials, unsigned int *tickets) {
+  CUMPSGEMM_CHAIN_HEAD_ENTRY();
   const unsigned int w = blockIdx.x >= d.grid_a ? 1u : 0u;
   const unsigned int bid = w ? blockIdx.x - d.grid_a : blockIdx.x;
   const unsigned int nb = w ? gridDim.x - d.grid_a : d.grid_a;
@@ -644,9 +647,9 @@ void exp_stats_pair(cuMpSGEMM_handle *h, bool full, unsigned id_a, unsigned am, 
   fused_stage1_dual_kernel<<<grid, THREADS, 0, h->cuda_stream>>>(
       d, es.ignore_threshold, es.underflow_threshold, es.underflow_tolerance_rate,
       scan_partials(h), scan_tickets(h));
-  fused_stage2_dual_kernel<<<grid, THREADS, 0, h->cuda_stream>>>(
-      d, es.ignore_threshold / 2, es.underflow_threshold / 2, es.underflow_tolerance_rate,
-      scan_partials(h), scan_tickets(h));
+  launch_chained(fused_stage2_dual_kernel, grid, THREADS, 0, h->cuda_stream, d,
+                 es.ignore_threshold / 2, es.underflow_threshold / 2, es.underflow_tolerance_rate,
+                 scan_partials(h), scan_tickets(h));
 }
 
 #define INSTANTIATE(T)                                                                           \

@@ -228,6 +228,36 @@ cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream
 cudaError_t launch_split_pair_auto(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream);
 
 // ---------------------------------------------------------------- TCEC GEMM
+// Launch behind the previous kernel of the stream with programmatic stream serialization: the
+// new grid may be scheduled while that kernel drains (which hides the launch latency of the short
+// kernels an AUTO / FP16TCEC_SCALING call chains: statistics -> constants -> split -> GEMM).
+// Every kernel launched this way executes griddepcontrol.wait before it reads or writes global
+// memory and only then griddepcontrol.launch_dependents, so completion stays transitive along
+// the chain and nothing runs ahead of data it depends on.
+#ifdef __CUDACC__
+template <class Kernel, class... Args>
+inline cudaError_t launch_chained(Kernel kernel, unsigned grid, unsigned block, std::size_t smem,
+                                  cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+// First statements of a kernel that is launched with launch_chained (harmless otherwise).
+#define CUMPSGEMM_CHAINED_KERNEL_ENTRY()                          \
+  asm volatile("griddepcontrol.wait;" ::: "memory");             \
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+// First statement of a kernel that heads a chain (ordinary launch).
+#define CUMPSGEMM_CHAIN_HEAD_ENTRY() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+#endif
+
 struct TcecGemmArgs {
   SplitKind kind;
   bool error_correction;

@@ -359,9 +359,10 @@ struct SplitJob {
 template <int KIND, bool VEC>
 __global__ void __launch_bounds__(THREADS, VEC ? 5 : 6) split_dual_kernel(const SplitJob a, const SplitJob b) {
   __shared__ float tile[TILE][TILE + 1]; // transposing staging tile shared by all paths
+  // Chained behind the kernel that writes the scaling constants (AUTO / FP16TCEC_SCALING), and
   // the GEMM kernel that follows may be scheduled while this one drains: its prologue does not
-  // depend on the panels, and its first panel load waits for this grid to complete
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // depend on the panels, and its first panel load waits for this grid to complete.
+  CUMPSGEMM_CHAINED_KERNEL_ENTRY();
   const uint32_t blocks_a = a.gx * a.gy * a.gz;
   uint32_t id = blockIdx.x;
   const SplitJob &j = (id < blocks_a) ? a : b;
@@ -378,7 +379,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(THREADS, VEC ? 5 : 6)
     split_dual_auto_kernel(const SplitJob a, const SplitJob b) {
   __shared__ float tile[TILE][TILE + 1];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // see split_dual_kernel
+  CUMPSGEMM_CHAINED_KERNEL_ENTRY(); // see split_dual_kernel
   const uint32_t blocks_a = a.gx * a.gy * a.gz;
   uint32_t id = blockIdx.x;
   const SplitJob &j = (id < blocks_a) ? a : b;
@@ -438,9 +439,8 @@ cudaError_t launch_split_pair_auto(const SplitArgs &a, const SplitArgs &b, cudaS
   if (blocks == 0 || blocks > 0x7fffffffull) return cudaErrorInvalidValue;
   const bool vec = (ja.path >= kPathKContig) || (jb.path >= kPathKContig);
   const unsigned grid = static_cast<unsigned>(blocks);
-  if (vec) split_dual_auto_kernel<true><<<grid, THREADS, 0, stream>>>(ja, jb);
-  else split_dual_auto_kernel<false><<<grid, THREADS, 0, stream>>>(ja, jb);
-  return cudaGetLastError();
+  if (vec) return launch_chained(split_dual_auto_kernel<true>, grid, THREADS, 0, stream, ja, jb);
+  return launch_chained(split_dual_auto_kernel<false>, grid, THREADS, 0, stream, ja, jb);
 }
 
 cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream_t stream) {
@@ -453,13 +453,11 @@ cudaError_t launch_split_pair(const SplitArgs &a, const SplitArgs &b, cudaStream
   const bool vec = (ja.path >= kPathKContig) || (jb.path >= kPathKContig);
   const unsigned grid = static_cast<unsigned>(blocks);
   if (a.kind == SplitKind::fp16) {
-    if (vec) split_dual_kernel<0, true><<<grid, THREADS, 0, stream>>>(ja, jb);
-    else split_dual_kernel<0, false><<<grid, THREADS, 0, stream>>>(ja, jb);
-  } else {
-    if (vec) split_dual_kernel<1, true><<<grid, THREADS, 0, stream>>>(ja, jb);
-    else split_dual_kernel<1, false><<<grid, THREADS, 0, stream>>>(ja, jb);
+    if (vec) return launch_chained(split_dual_kernel<0, true>, grid, THREADS, 0, stream, ja, jb);
+    return launch_chained(split_dual_kernel<0, false>, grid, THREADS, 0, stream, ja, jb);
   }
-  return cudaGetLastError();
+  if (vec) return launch_chained(split_dual_kernel<1, true>, grid, THREADS, 0, stream, ja, jb);
+  return launch_chained(split_dual_kernel<1, false>, grid, THREADS, 0, stream, ja, jb);
 }
 
 } // namespace cumpsgemm_b200
