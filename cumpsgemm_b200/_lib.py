@@ -90,6 +90,8 @@ PROTOTYPES = {
     "cuMpSGEMM_set_workspace_limit": (None, [vp, C.c_size_t]),
     "cuMpSGEMM_set_count_tail_padding": (None, [vp, i32]),
     "cuMpSGEMM_reload_tuning_env": (None, [vp]),
+    "cuMpSGEMM_plan_pair_tail": (i32, [u32, u32, u32, i32, C.POINTER(u32), C.POINTER(u32),
+                                       C.POINTER(u32), C.POINTER(u32)]),
     "cuMpSGEMM_set_debug_buffer": (None, [vp, vp]),
     "cuMpSGEMM_set_kernel_timing": (None, [vp, i32]),
     "cuMpSGEMM_get_kernel_timing": (C.c_ulonglong, [vp, C.POINTER(C.c_double),

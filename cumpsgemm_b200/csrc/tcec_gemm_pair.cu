@@ -711,3 +711,30 @@ cudaError_t launch_tcec_gemm_pair_auto(const TcecGemmArgs &a, cudaStream_t strea
 }
 
 } // namespace cumpsgemm_b200
+
+extern "C" int cuMpSGEMM_plan_pair_tail(unsigned total_tiles, unsigned clusters, unsigned k_pad,
+                                        int tf32, unsigned *split_begin, unsigned *slices,
+                                        unsigned *slice_k, unsigned *work_items) {
+  using namespace cumpsgemm_b200;
+  if (total_tiles == 0 || clusters == 0 || k_pad == 0 || k_pad % 64 != 0 ||
+      split_begin == nullptr || slices == nullptr || slice_k == nullptr || work_items == nullptr)
+    return 1;
+  const SplitKind kind = tf32 ? SplitKind::tf32 : SplitKind::fp16;
+  const unsigned k_per_stage = ROW_BYTES / (tf32 ? 4u : 2u);
+  // the plan only looks at whether scratch and counters exist, never at their contents
+  static float scratch_marker;
+  static unsigned int counter_marker[2];
+  TcecGemmArgs a = {};
+  a.tail_partial = &scratch_marker;
+  a.wave_counter = counter_marker;
+  a.tuning = Tuning{};
+  GemmKernelParams p = {};
+  p.total_tiles = total_tiles;
+  p.k_blocks = k_pad / k_per_stage;
+  const PairTail t = plan_tail(a, kind, p, clusters);
+  *split_begin = t.split_begin;
+  *slices = t.slices;
+  *slice_k = t.slice_blocks * k_per_stage;
+  *work_items = t.work_items;
+  return 0;
+}

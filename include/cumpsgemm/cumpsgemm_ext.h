@@ -144,9 +144,20 @@ void cuMpSGEMM_set_workspace_limit(cuMpSGEMM_handle_t handle, size_t bytes);
  * such shapes too; with it off only real matrix elements are counted. */
 void cuMpSGEMM_set_count_tail_padding(cuMpSGEMM_handle_t handle, int enable);
 /* A handle reads the tuning variables (CUMPSGEMM_TILE_N, CUMPSGEMM_PAIR, CUMPSGEMM_DRAIN_CHUNK,
- * CUMPSGEMM_FIRST_CHUNK, CUMPSGEMM_PACE, CUMPSGEMM_FUSED) once, when it is created, so that a
- * GEMM call does not query the environment; this reads them again. */
+ * CUMPSGEMM_FIRST_CHUNK, CUMPSGEMM_PACE, CUMPSGEMM_FUSED, CUMPSGEMM_SPLIT_K,
+ * CUMPSGEMM_TAIL_SPLIT) once, when it is created, so that a GEMM call does not query the
+ * environment; this reads them again. */
 void cuMpSGEMM_reload_tuning_env(cuMpSGEMM_handle_t handle);
+/* Host-only query (no GPU needed): how the CTA-pair kernel would schedule `total_tiles` tiles
+ * of 256 x 256 with a K loop of k_pad values (a multiple of 64; tf32 != 0 for the TF32 kinds) on
+ * `clusters` CTA pairs.  Tiles [0, *split_begin) run whole; each later tile (the last, partly
+ * filled wave) is cut into *slices K slices of *slice_k values, *work_items work items in
+ * all.  *slices == 1: nothing is cut.  Returns 0, or 1 for invalid arguments.  No counterpart
+ * in the reference (its atomic split-K kernel, src/cumpsgemm.cu:272-304, is the nearest
+ * relative). */
+int cuMpSGEMM_plan_pair_tail(unsigned total_tiles, unsigned clusters, unsigned k_pad, int tf32,
+                             unsigned *split_begin, unsigned *slices, unsigned *slice_k,
+                             unsigned *work_items);
 /* Per-launch device timing with CUDA events on the handle's stream (off by default).  While
  * enabled every split + GEMM launch group records three events; get_kernel_timing
  * synchronises the stream, returns the number of launch groups since the last query and the

@@ -153,3 +153,46 @@ def test_create_without_gpu_fails_loudly(clib):
 
     with pytest.raises(api.CuMpSGEMMError):
         api.Handle()
+
+
+def test_pair_tail_plan_host_logic():
+    """How the CTA-pair kernel cuts the last, partly filled wave of tiles into K slices (a
+    host-only query of the library, no GPU): every tile is covered exactly once, the slices
+    of the cut tiles fit the clusters of one wave, a slice keeps at least 1024 k values, and
+    nothing is cut when the last wave is more than half full or K is short."""
+    import ctypes as C
+
+    from cumpsgemm_b200 import _lib
+
+    lib = _lib.load()
+
+    def plan(tiles, clusters, k, tf32=0):
+        out = [C.c_uint32() for _ in range(4)]
+        assert lib.cuMpSGEMM_plan_pair_tail(tiles, clusters, k, tf32, *map(C.byref, out)) == 0
+        return tuple(o.value for o in out)
+
+    # m=n=k=4096 on 74 clusters: 256 tiles = 3 full waves + 34 tiles, cut in two
+    assert plan(256, 74, 4096) == (222, 2, 2048, 222 + 34 * 2)
+    assert plan(256, 74, 4096, 1) == (222, 2, 2048, 290)
+    # m=n=k=16384: 4096 tiles, 26 in the last wave
+    assert plan(4096, 74, 16384) == (4070, 2, 8192, 4070 + 52)
+    # last wave more than half full, exactly full, or K too short for two slices: nothing is cut
+    assert plan(1024, 74, 8192) == (1024, 1, 8192, 1024)
+    assert plan(148, 74, 8192) == (148, 1, 8192, 148)
+    assert plan(256, 74, 1024) == (256, 1, 1024, 256)
+    # four tiles and a long K: eight slices at most
+    sb, sl, sk, wi = plan(4, 74, 8192 + 64)
+    assert (sb, sl, wi) == (0, 8, 32) and sk * sl >= 8192 + 64 and sk * (sl - 1) < 8192 + 64
+    for tiles in (1, 5, 37, 38, 75, 100, 111, 300, 1000):
+        for clusters in (1, 2, 66, 74):
+            for k in (64, 1024, 2048, 3072, 65536):
+                for tf32 in (0, 1):
+                    sb, sl, sk, wi = plan(tiles, clusters, k, tf32)
+                    rem = tiles - sb
+                    assert wi == sb + rem * sl and 1 <= sl <= 8
+                    if sl > 1:
+                        assert sb % clusters == 0 and rem * sl <= clusters and 2 * rem <= clusters
+                        assert sk >= 1024 and sk * sl >= k and sk * (sl - 1) < k
+                    else:
+                        assert sb == tiles and sk == k
+    assert lib.cuMpSGEMM_plan_pair_tail(0, 74, 4096, 0, None, None, None, None) == 1
