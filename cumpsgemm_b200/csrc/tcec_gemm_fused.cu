@@ -46,7 +46,9 @@
 // trip.  Two converter teams taking the stages in turn (one team's latency under the other's
 // conversion) were tried and measured slower (0.59 against 0.38 ms): three stages of 64 KiB
 // are all that fit, and with two of them being converted a team always needs the stage the
-// tensor core has only just received from the other team.
+// tensor core has only just received from the other team.  The two operands' warps converting
+// in turns (loads issued before the wait for the turn) measured 0.66 ms: a warp's conversion is
+// bound by its own instruction latency, not by issue slots, so taking turns only serialises it.
 //
 // Operand layouts the converters understand (anything else takes the pre-split path):
 //   kcontig  element (r, kk) of the real operand at src[r * ld + kk]      (A with op T, B with
