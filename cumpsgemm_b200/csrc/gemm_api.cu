@@ -116,7 +116,16 @@ bool fused_args(const cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperati
     // its workspace traffic and a second launch weigh as much as the products; a single
     // matrix, large tiles counts or a long K loop are better off pre-split (every operand
     // element is converted once per tile that uses it).
-    if (batch < 8 || m_exp > 512 || n > 512 || k_exp > 1024) return false;
+    // A handful of tiles and a very long K loop: this kernel with its K loop cut over the SMs
+    // (split-K below) against the pre-split split-K path, ms per call, NN:
+    //   256 x 256 x 65536   0.068 / 0.085     128 x 128 x 131072   0.054 / 0.080
+    //   384 x 384 x 32768   0.070 / 0.079     256 x 256 x 8192     0.021 / 0.025
+    //   512 x 512 x 16384   0.064 / 0.056 (sixteen tiles: the pre-split path wins again)
+    // There the split pass alone moves twice the operand bytes the products need.
+    const std::uint64_t tiles = ((m_exp + 127) / 128) * ((n + 127) / 128) * batch;
+    const bool few_long = h->tuning.split_k != 0 && h->tuning.pair != 1 &&
+                          h->tuning.tile_n != 256 && tiles <= 9 && k_exp >= 8192;
+    if (!few_long && (batch < 8 || m_exp > 512 || n > 512 || k_exp > 1024)) return false;
   }
   out->a = reinterpret_cast<const float *>(a);
   out->b = reinterpret_cast<const float *>(b);
@@ -138,6 +147,24 @@ bool fused_args(const cuMpSGEMM_handle *h, cublasOperation_t op_A, cublasOperati
   out->is_complex = is_complex;
   out->tile_n = (h->tuning.tile_n == 64 || n <= 64) ? 64 : 128;
   out->tuning = h->tuning;
+  // split-K when the tiles leave at least half of the SMs idle and K is long: as many slices
+  // as fill the GPU, each at least four stages (256 k values) long
+  out->k_slices = 1;
+  out->partial = nullptr;
+  {
+    const std::uint64_t tiles =
+        ((m_exp + 127) / 128) * ((n + out->tile_n - 1) / out->tile_n) * batch;
+    const std::uint64_t stages = (k_exp + 63) / 64;
+    if (h->tuning.split_k != 0 && 2 * tiles <= h->num_sms && stages >= 8) {
+      std::uint64_t want = h->num_sms / tiles;
+      if (h->tuning.split_k > 1) want = static_cast<std::uint64_t>(h->tuning.split_k);
+      want = std::min<std::uint64_t>(want, stages / 4);
+      if (want > 1) {
+        const std::uint64_t per = (stages + want - 1) / want;
+        out->k_slices = static_cast<std::uint32_t>((stages + per - 1) / per);
+      }
+    }
+  }
   return true;
 }
 
@@ -218,7 +245,16 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
     fa.beta_i = Scalar<T>::im(beta);
     fa.dyn = dyn;
     fa.dev_status = h->dev_status;
-    if (used_kernel_module_id != nullptr) *used_kernel_module_id = (fa.tile_n == 128) ? 1u : 2u;
+    if (fa.k_slices > 1) {
+      const std::size_t bytes = static_cast<std::size_t>(fa.k_slices) * fa.m * fa.n * fa.batch *
+                                sizeof(float);
+      const std::size_t limit =
+          h->workspace_limit_bytes ? h->workspace_limit_bytes : kDefaultWorkspaceLimit;
+      if (bytes > limit || !ensure_workspace(h, bytes)) fa.k_slices = 1; // no room: no split
+      else fa.partial = reinterpret_cast<float *>(h->workspace);
+    }
+    if (used_kernel_module_id != nullptr)
+      *used_kernel_module_id = (fa.k_slices > 1) ? 100u : (fa.tile_n == 128) ? 1u : 2u;
     const bool prof = h->exp_stats.profiling_enabled;
     if (prof) h->exp_stats.profiler.start("gemm_kernel", h->cuda_stream);
     cuMpSGEMM_handle::TimingTriple tt{};
@@ -227,7 +263,25 @@ cublasStatus_t gemm_dispatch(cuMpSGEMM_handle *h, cublasOperation_t op_A, cublas
       cudaEventRecord(tt.e[0], h->cuda_stream);
       cudaEventRecord(tt.e[1], h->cuda_stream);
     }
-    const cudaError_t ferr = launch_tcec_gemm_fused(fa, h->cuda_stream);
+    cudaError_t ferr = launch_tcec_gemm_fused(fa, h->cuda_stream);
+    if (ferr == cudaSuccess && fa.k_slices > 1) {
+      TcecGemmArgs r = {};
+      r.m = fa.m;
+      r.n = fa.n;
+      r.batch = fa.batch;
+      r.c = fa.c;
+      r.ldc = fa.ldc;
+      r.stride_c = fa.stride_c;
+      r.alpha_r = fa.alpha_r;
+      r.alpha_i = fa.alpha_i;
+      r.beta_r = fa.beta_r;
+      r.beta_i = fa.beta_i;
+      r.is_complex = fa.is_complex;
+      r.dyn = fa.dyn;
+      r.k_slices = fa.k_slices;
+      r.partial = fa.partial;
+      ferr = launch_splitk_reduce(r, h->cuda_stream);
+    }
     if (h->kernel_timing) {
       cudaEventRecord(tt.e[2], h->cuda_stream);
       h->timing_events.push_back(tt);

@@ -326,6 +326,11 @@ struct FusedGemmArgs {
   int *dev_status;
   int tile_n; // 128 or 64
   Tuning tuning;
+  // Split-K: k_slices > 1 cuts every tile's K loop into that many CTAs, which write plain
+  // partial sums to `partial` (k_slices * batch * m * n floats, [slice][batch][column][row]);
+  // the caller then runs launch_splitk_reduce, which applies alpha, beta and the un-scaling.
+  std::uint32_t k_slices = 1;
+  float *partial = nullptr;
 };
 cudaError_t launch_tcec_gemm_fused(const FusedGemmArgs &a, cudaStream_t stream);
 // Self-test of the bounded mbarrier wait (see cuMpSGEMM_selftest_bounded_wait).

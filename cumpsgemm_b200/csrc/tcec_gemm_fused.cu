@@ -515,6 +515,27 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t tile, const GemmKernelP
   return c;
 }
 
+// Work item w of a launch: tile w with its whole K loop, or, with split-K, slice w % k_slices
+// (stages [kb0, kb0 + kbn) of the K loop) of tile w / k_slices.
+struct WorkItem {
+  uint32_t tile, kb0, kbn, slice;
+};
+__device__ __forceinline__ WorkItem work_item(uint32_t w, const GemmKernelParams &p) {
+  WorkItem x;
+  if (p.k_slices <= 1) {
+    x.tile = w;
+    x.kb0 = 0;
+    x.kbn = p.k_blocks;
+    x.slice = 0;
+  } else {
+    x.tile = w / p.k_slices;
+    x.slice = w - x.tile * p.k_slices;
+    x.kb0 = x.slice * p.slice_blocks;
+    x.kbn = min(p.slice_blocks, p.k_blocks - x.kb0);
+  }
+  return x;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const FusedParams fp,
                                                                          const GemmKernelParams p) {
@@ -544,6 +565,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t total_tiles = p.total_tiles;
+  const uint32_t total_work = total_tiles * p.k_slices; // work items of the launch
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -588,8 +610,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
       constexpr uint32_t IDESC2 = ptx::make_idesc(0, BM, 2 * BN);
       uint32_t s = 0, ph = 0, chunk_idx = 0;
       uint32_t started = 0;
-      for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (uint32_t w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         *tiles_started = ++started;
+        const uint32_t k_blocks = work_item(w, p).kbn; // stages of this work item
         uint32_t chunk_end = 0; // first stage after the current chunk
         for (uint32_t kb = 0; kb < k_blocks; ++kb) {
           const bool first_in_chunk = (kb == chunk_end);
@@ -642,7 +665,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
       const uint32_t t = threadIdx.x - (MMA_WARP + 1) * 32;
       constexpr uint32_t PF_THREADS = (NUM_THREADS / 32 - MMA_WARP - 1) * 32;
       uint32_t it = 0;
-      for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      // (not with split-K: a work item then reads one K slice of its tile only)
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && p.k_slices <= 1; tile += gridDim.x) {
         ++it;
         uint32_t polls = 0;
         while (*tiles_started < it && !*abort_flag && ++polls < (1u << 22)) __nanosleep(256);
@@ -675,8 +699,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
                                                                : (KS / 2) * o.ld;
     uint32_t s = 0, ph = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const TileCoord tc = tile_coord<BN>(tile, p);
+    for (uint32_t w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const WorkItem wi = work_item(w, p);
+      const uint32_t k_blocks = wi.kbn;
+      const TileCoord tc = tile_coord<BN>(wi.tile, p);
       const uint32_t row0 = for_a ? tc.m0 : tc.n0;
       const float *src = o.src + static_cast<uint64_t>(tc.batch) * o.stride;
       const bool rows_inside = row0 + rows_tile <= o.rows;
@@ -688,6 +714,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
         lp = src + static_cast<uint64_t>(pl.g_k) * o.ld + row0 + pl.g_row;
       else
         lp = src + static_cast<uint64_t>(pl.g_k >> 1) * o.ld + row0 + pl.g_row;
+      lp += static_cast<uint64_t>(wi.kb0) * stage_step;
       for (uint32_t kb = 0; kb < k_blocks; ++kb, lp += stage_step) {
         if (lane == 0)
           ok = ptx::mbar_wait_poll(ptx::smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status,
@@ -695,7 +722,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         const uint32_t hi_tile = ptx::smem_u32(smem + s * Cfg::STAGE_BYTES) + tile_off;
-        const uint32_t k0 = kb * KS;
+        const uint32_t k0 = (wi.kb0 + kb) * KS;
         if (rows_inside && k0 + KS <= fp.k) {
           const uint32_t hi_addr = hi_tile + pl.st_off;
           if (o.layout == kLayoutKContig) {
@@ -738,11 +765,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
     const uint32_t half = static_cast<uint32_t>((warp - FIRST_EPI_WARP) >> 2);
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const uint32_t col_base = half * CPT;
-    const uint32_t n_chunks =
-        1u + ((k_blocks > p.first_chunk)
-                  ? (k_blocks - p.first_chunk + p.drain_chunk - 1) / p.drain_chunk
-                  : 0u);
-    const float unscale = (p.dyn != nullptr) ? p.dyn->unscale_c : 1.f;
+    // with split-K the un-scaling belongs to the reduction kernel, like alpha and beta
+    const float unscale = (p.dyn != nullptr && p.k_slices <= 1) ? p.dyn->unscale_c : 1.f;
     const float ar = p.alpha_r * unscale, ai = p.alpha_i * unscale;
     const float br = p.beta_r, bi = p.beta_i;
     const bool read_c = (br != 0.f) || (bi != 0.f);
@@ -751,14 +775,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) tcec_gemm_fused_kernel(const F
 
     uint32_t chunk_idx = 0;
     bool ok = true;
-    for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const TileCoord tc = tile_coord<BN>(tile, p);
+    for (uint32_t w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const WorkItem wi = work_item(w, p);
+      const uint32_t n_chunks =
+          1u + ((wi.kbn > p.first_chunk)
+                    ? (wi.kbn - p.first_chunk + p.drain_chunk - 1) / p.drain_chunk
+                    : 0u);
+      const TileCoord tc = tile_coord<BN>(wi.tile, p);
       float acc[CPT];
 #pragma unroll
       for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
       const uint32_t row = tc.m0 + quarter * 32u + static_cast<uint32_t>(lane);
       const bool row_ok = row < p.m;
-      float *cbase = p.c + static_cast<uint64_t>(tc.batch) * p.stride_c + row;
+      // (split-K: p.c is the scratch for partial sums, one block of all tiles per slice)
+      float *cbase = p.c + static_cast<uint64_t>(wi.slice) * p.slice_stride +
+                     static_cast<uint64_t>(tc.batch) * p.stride_c + row;
 
       for (uint32_t c = 0; c < n_chunks; ++c, ++chunk_idx) {
         const uint32_t b0 = chunk_idx & 1u;
@@ -927,8 +958,31 @@ cudaError_t launch_fused_variant(const FusedGemmArgs &a, cudaStream_t stream) {
   const uint64_t total = static_cast<uint64_t>(p.tiles_m) * p.tiles_n * a.batch;
   if (total == 0 || total > 0x7fffffffull) return cudaErrorInvalidValue;
   p.total_tiles = static_cast<uint32_t>(total);
+  p.k_slices = 1;
+  p.slice_blocks = p.k_blocks;
+  p.slice_stride = 0;
+  if (a.k_slices > 1) {
+    // plain partial sums into the caller's scratch, [slice][batch][column][row]; alpha, beta,
+    // complex arithmetic and the un-scaling are the reduction kernel's
+    if (a.partial == nullptr || a.k_slices > 0xffffu) return cudaErrorInvalidValue;
+    p.slice_blocks = (p.k_blocks + a.k_slices - 1) / a.k_slices;
+    const uint32_t slices = (p.k_blocks + p.slice_blocks - 1) / p.slice_blocks;
+    if (slices != a.k_slices) return cudaErrorInvalidValue; // the caller sized the scratch
+    p.k_slices = static_cast<uint16_t>(slices);
+    p.c = a.partial;
+    p.ldc = a.m;
+    p.stride_c = static_cast<uint64_t>(a.m) * a.n;
+    p.slice_stride = p.stride_c * a.batch;
+    p.alpha_r = 1.f;
+    p.alpha_i = 0.f;
+    p.beta_r = 0.f;
+    p.beta_i = 0.f;
+    p.is_complex = 0;
+  }
+  const uint64_t work = total * p.k_slices;
+  if (work > 0x7fffffffull) return cudaErrorInvalidValue;
   const unsigned grid = static_cast<unsigned>(
-      total < static_cast<uint64_t>(num_sms[dev]) ? total : num_sms[dev]);
+      work < static_cast<uint64_t>(num_sms[dev]) ? work : num_sms[dev]);
   kernel<<<grid, NUM_THREADS, Cfg::SMEM_BYTES, stream>>>(fp, p);
   return cudaGetLastError();
 }

@@ -230,3 +230,71 @@ def test_run_to_run_determinism(handle, oracle):
         handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c1, m, FP16TCEC)
         handle.gemm(N, N, m, n, k, 1.0, a, m, b, k, 0.0, c2, m, FP16TCEC)
     assert torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("case", ["real_tn", "real_nn_ragged", "complex", "scaling_batch"])
+def test_split_k_inside_the_on_the_fly_kernel(handle, oracle, case):
+    """Few tiles and a long K loop on the on-the-fly route: the kernel's K loop is cut into
+    slices over the SMs, every slice writes plain partial sums, the reduction kernel adds them
+    in ascending order and applies alpha, beta (complex too) and the un-scaling.  Reported as
+    module 100, bit-identical from run to run, inside the pass criterion, and the default rule
+    takes this route by itself for a handful of tiles with k >= 8192."""
+    import torch
+
+    if case == "real_tn":
+        m, n, k, op_a = 256, 128, 8192 + 64, T
+        a, b = oracle.gen_uniform(1, m * k), oracle.gen_uniform(2, k * n)
+        c0 = oracle.gen_uniform(3, m * n)
+        da, db = _dev(a), _dev(b)
+        truth = oracle.gemm_f64(op_a, N, m, n, k, 1.5, a, k, b, k, -0.5, c0, m)
+        outs = []
+        for rep in range(2):
+            dc = _dev(c0.copy())
+            st, mod = handle.gemm_module(op_a, N, m, n, k, 1.5, da, k, db, k, -0.5, dc, m, FP16TCEC)
+            assert st == 0 and mod == 100          # the default rule, nothing forced
+            outs.append(dc)
+        assert torch.equal(outs[0], outs[1])
+        assert oracle.residual(truth, outs[0].cpu().numpy(), m) < oracle.error_threshold(True, k)
+        _, split = _both_paths(
+            handle, lambda c: handle.gemm(op_a, N, m, n, k, 1.5, da, k, db, k, -0.5, c, m, FP16TCEC), c0)
+        assert _close(outs[0].cpu().numpy(), split, m)
+    elif case == "real_nn_ragged":
+        m, n, k = 200, 72, 2500                    # forced: edge tiles, K not a multiple of 64
+        lda, ldb, ldc = 200, 2500, 203
+        a, b = oracle.gen_uniform(4, lda * k), oracle.gen_uniform(5, ldb * n)
+        c0 = oracle.gen_uniform(6, ldc * n)
+        da, db = _dev(a), _dev(b)
+        truth = oracle.gemm_f64(N, N, m, n, k, 1.0, a, lda, b, ldb, 0.25, c0, ldc)
+        with _Fused(handle, "1"):
+            dc = _dev(c0.copy())
+            st, mod = handle.gemm_module(N, N, m, n, k, 1.0, da, lda, db, ldb, 0.25, dc, ldc, FP16TCEC)
+            assert st == 0 and mod == 100
+        assert oracle.residual(truth, dc.cpu().numpy(), ldc) < oracle.error_threshold(True, k)
+    elif case == "complex":
+        m, n, k = 96, 64, 4100
+        gen = lambda s, cnt: (oracle.gen_uniform(s, cnt) + 1j * oracle.gen_uniform(s + 50, cnt)).astype(np.complex64)
+        a, b, c0 = gen(7, m * k), gen(8, k * n), gen(9, m * n)
+        da, db = _dev(a), _dev(b)
+        alpha, beta = 0.5 - 1.5j, -0.25 + 2j
+        truth = oracle.gemm_f64(N, N, m, n, k, alpha, a, m, b, k, beta, c0, m)
+        with _Fused(handle, "1"):
+            dc = _dev(c0.copy())
+            assert handle.gemm(N, N, m, n, k, alpha, da, m, db, k, beta, dc, m, FP16TCEC) == 0
+        assert oracle.residual(truth, dc.cpu().numpy(), m) < oracle.error_threshold(True, k)
+    else:
+        batch, m, n, k = 3, 128, 128, 2048         # tiny operands: the un-scaling is the reduction's
+        a = (oracle.gen_uniform(10, batch * m * k) * np.float32(2.0 ** -24)).astype(np.float32)
+        b = (oracle.gen_uniform(11, batch * k * n) * np.float32(2.0 ** -20)).astype(np.float32)
+        c0 = np.zeros(batch * m * n, dtype=np.float32)
+        da, db = _dev(a), _dev(b)
+        with _Fused(handle, "1"):
+            dc = _dev(c0.copy())
+            assert handle.gemm_strided_batch(T, N, m, n, k, 1.0, da, k, m * k, db, k, k * n, 0.0, dc,
+                                             m, m * n, batch, SCALING) == 0
+        res = dc.cpu().numpy()
+        for i in range(batch):
+            truth = oracle.gemm_f64(T, N, m, n, k, 1.0, a[i * m * k:], k, b[i * k * n:], k, 0.0,
+                                    c0[i * m * n:], m)
+            assert oracle.residual(truth, res[i * m * n:(i + 1) * m * n], m) < \
+                oracle.error_threshold(True, k)
+    assert handle.kernel_status() == 0
