@@ -17,7 +17,11 @@
 // and reading them back is most of the traffic.  It loses for long K on large matrices, where
 // every operand element is converted once per tile that uses it (n / BN times for A, m / 128
 // times for B) and the converter warps, not the tensor core, set the pace; the dispatch keeps
-// the pre-split path there.
+// the pre-split path there.  A second regime is a handful of tiles with a very long K loop:
+// the launch's work items are then (tile, K slice) pairs, every slice writes plain partial
+// sums, and splitk_reduce_kernel (tcec_gemm.cu) adds them in ascending order and applies alpha,
+// beta and the un-scaling — the deterministic successor of the reference's atomic split-K
+// kernel (src/cumpsgemm.cu:272-304) without a split pass in front.
 //
 // Roles (896 threads = 7 warpgroups): warps 0-3 and 12-23 = 16 converter warps (eight for the
 // A tile, eight for the B tile of every stage), warps 4-11 = accumulator drain + epilogue
