@@ -95,7 +95,8 @@ enum : int {
   kErrWaitD0Full = 4,  // epilogue waited for a chunk's main accumulator
   kErrWaitD1Full = 5,  // epilogue waited for the correction accumulator
   kErrBadLaunch = 6,
-  kErrWaitD1Empty = 7  // MMA issuer waited for the epilogue to read the correction accumulator
+  kErrWaitD1Empty = 7, // MMA issuer waited for the epilogue to read the correction accumulator
+  kErrWaitTail = 8     // epilogue warps of a CTA waited for one another (tail split of the pair kernel)
 };
 
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s
@@ -176,11 +177,6 @@ __device__ __forceinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity,
   const bool ok = mbar_wait(bar, parity, abort_smem, status_gmem, code);
   *acc += static_cast<unsigned long long>(clock64() - t0);
   return ok;
-}
-
-// Barrier `id` (1..15; 0 is __syncthreads) over `count` threads of the CTA (a multiple of 32).
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization

@@ -149,7 +149,8 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
   uint64_t *d0_empty = bars + 2 * STAGES + 1;
   uint64_t *d1_full = bars + 2 * STAGES + 2;
   uint64_t *d1_empty = bars + 2 * STAGES + 3;
-  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  uint64_t *tail_bar = bars + 2 * STAGES + 4; // the eight epilogue warps of this CTA (tail split)
+  uint32_t *tmem_base_ptr = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_base_ptr + 1);
   volatile uint32_t *ticket_smem = reinterpret_cast<volatile uint32_t *>(tmem_base_ptr + 2);
 
@@ -170,6 +171,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
     ptx::mbar_init(ptx::smem_u32(d0_empty), 2 * NUM_EPI_WARPS);
     ptx::mbar_init(ptx::smem_u32(d1_full), 1);
     ptx::mbar_init(ptx::smem_u32(d1_empty), 2 * NUM_EPI_WARPS);
+    ptx::mbar_init(ptx::smem_u32(tail_bar), NUM_EPI_WARPS);
     *abort_flag = 0;
     ptx::mbar_init_fence();
     ptx::prefetch_tensormap(&map_a);
@@ -326,7 +328,7 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
     const float sgn = (lane & 1) ? 1.f : -1.f; // odd rows hold imaginary parts
     const float lsi = p.lo_scale_inv;
 
-    uint32_t chunk_idx = 0, tile_iter = 0;
+    uint32_t chunk_idx = 0, tile_iter = 0, tail_phase = 0;
     bool ok = true;
     for (uint32_t w = cluster_id; w < work_items && ok; w += num_clusters, ++tile_iter) {
       const WorkItem wi = work_item(w, tail, k_blocks);
@@ -409,9 +411,21 @@ __device__ __forceinline__ void pair_body(const CUtensorMap &map_a, const CUtens
 #pragma unroll
         for (int i = 0; i < CPT; ++i) __stcg(mine + (col_base + i) * BM_CTA, acc[i]);
         __threadfence();
-        ptx::named_bar_sync(1, NUM_EPI_WARPS * 32);
+        // the eight epilogue warps meet twice (all partial sums stored; ticket published) on
+        // an mbarrier of their own, with the bounded wait every other wait here uses
+        auto meet = [&]() -> bool {
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(tail_bar));
+          const bool met = ptx::mbar_wait(ptx::smem_u32(tail_bar), tail_phase, abort_flag,
+                                          p.status, ptx::kErrWaitTail);
+          tail_phase ^= 1u;
+          return met;
+        };
+        ok = meet();
+        if (!ok) break;
         if (warp == 4 && lane == 0) *ticket_smem = atomicAdd(tail.counters + ti * 2u + rank, 1u);
-        ptx::named_bar_sync(1, NUM_EPI_WARPS * 32);
+        ok = meet();
+        if (!ok) break;
         if (*ticket_smem != tail.slices - 1u) continue;
         __threadfence();
 #pragma unroll

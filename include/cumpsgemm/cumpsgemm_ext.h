@@ -123,7 +123,10 @@ cublasStatus_t cuMpSGEMM_sgemm_module(
 /* ---- kernel status -------------------------------------------------------- */
 /* Every wait inside the GEMM kernel is bounded; a wait that gives up records a non-zero
  * code in a device word.  This call synchronises the handle's stream, returns the word and
- * clears it.  0 = no error. */
+ * clears it.  0 = no error; 1 = a producer / converter waited for a free stage, 2 = the MMA
+ * issuer for operands, 3 / 7 = the MMA issuer for the drain of an accumulator, 4 / 5 = the
+ * epilogue for an accumulator, 6 = bad launch, 8 = the epilogue warps of a CTA for one another
+ * (tail split of the CTA-pair kernel). */
 int cuMpSGEMM_get_kernel_status(cuMpSGEMM_handle_t handle);
 /* Self-test of the bounded wait: a one-CTA kernel waits, with the same routine the GEMM kernels
  * use, on a barrier that nothing signals; after limit_ms it must give up, record its code and
